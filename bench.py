@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the attention / KV-cache hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at every N: BASELINE config 4 -- long-context decode, 1 sequence, q_len 1,
+24 query / 4 KV heads, head_dim 256, the token at position 131000 attends 131001 keys
+of a q4_0/q4_0 cache. One STEP is that token's attention in the engine's 16
+full-attention layers, each with its own K/V cache: per layer the new K/V row is
+appended (quantized) at position 131000, the split-KV decode kernel runs over the
+layer's cache, and the merge applies the fused sigmoid gate. Sixteen distinct caches
+(2.4 GB) are walked per step, so nothing is served from the 126 MB L2.
+
+metric/value: decode-attention HBM GB/s = algorithmic KV+Q+out bytes per step / step
+time, inputs resident in HBM, timed with CUDA events on the launching stream.
+e2e: the same through the C-ABI with HOST buffers -- per layer the q row, the gate row
+and the new K/V rows are copied from pinned host memory and the output is copied back,
+all inside the timed region.
+roofline: the decode kernel alone (records-only launches), CUDA events, against the
+measured HBM copy peak in MEASURED_PEAKS.json.
+cpu_baseline: the CPU oracle's attention (all host threads) on one layer of the same
+workload.
+
+With N > 1 (one process per GPU under torch.distributed.run) the context is sharded:
+rank r holds keys [r*ceil(n/N), ...) of every layer, computes one partial record per
+head, the records are all-gathered over NCCL and merged on every rank ("strong"
+scaling: the job is fixed, the per-GPU slice shrinks).
+"""
+import argparse
+import importlib
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NH, NKV, HD = 24, 4, 256
+N_LAYERS = 16
+POS = 131000
+N_KEYS = POS + 1
+MAX_CTX = 131072
+SCALE = 1.0 / 16.0
+KT = VT = 3  # q4_0
+
+
+def algorithmic_bytes(n_keys, row_k, row_v):
+    """Unique bytes of one layer-step: every K and V row once, Q in, out out."""
+    return n_keys * NKV * (row_k + row_v) + 2 * NH * HD * 4
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while a timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def reference_arm(args):
+    """The reference has no CPU implementation of this path in its engine (HIP only), and
+    its kernels run here only under a lock-step fiber emulator whose timing is
+    meaningless; the timed CPU arm is therefore the oracle port, on all host threads, on
+    one layer of the same workload per step."""
+    import numpy as np
+    from oracle.oracle import Oracle
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ora = Oracle()
+    cores = ora.num_threads()
+    kc = ora.kv_fill(KT, N_KEYS * NKV, HD, 11)
+    vc = ora.kv_fill(VT, N_KEYS * NKV, HD, 22)
+    q = ora.kv_fill_values(NH, HD, 3)
+    steps, warm = max(1, min(args.steps, 3)), max(0, min(args.warmup, 1))
+    for _ in range(warm):
+        ora.attn(q[None], kc, vc, [POS], NKV, SCALE, KT, VT)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ora.attn(q[None], kc, vc, [POS], NKV, SCALE, KT, VT)
+    dt = (time.perf_counter() - t0) / steps
+    row = ora.row_bytes(KT)
+    gbs = algorithmic_bytes(N_KEYS, row, row) / dt / 1e9
+    sample = "one layer of the workload (131001 keys, q4_0/q4_0) per step, CPU oracle with OpenMP"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_attn_hbm_gbs_128k_q4_0", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(n_gpus):
+    return {"workload": "decode q_len=1, ctx 131072 (pos 131000 -> 131001 keys), 24Q/4KV heads, hd 256, "
+                        "K,V q4_0, 16 layer caches per step",
+            "l2": "16 distinct 151 MB cache pairs walked per step (> 126 MB L2)",
+            "parallelism": f"context sharded over {n_gpus} GPU(s), NCCL all-gather of partial records"
+            if n_gpus > 1 else "1 GPU"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS, help=argparse.SUPPRESS)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rd = importlib.import_module("rdna4-infer_b200")
+    L = rd.lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    n_layers = args.layers
+    W = max(args.warmup, 3)
+    K = args.steps
+
+    # ---- this rank's slice of the context -------------------------------------------
+    per = (N_KEYS + world - 1) // world
+    kb, ke = rank * per, min(N_KEYS, (rank + 1) * per) - 1     # keys kb..ke inclusive
+    owns_new_row = kb <= POS <= ke
+    row = rd.row_bytes(KT)
+    slice_rows = max(ke - kb + 1, 0)
+    st = rd.stream_ptr()
+    # caches hold only this rank's slice; filled on the device with the synthetic hash
+    kcache = [torch.empty(max(slice_rows, 1) * NKV * row, dtype=torch.uint8, device="cuda") for _ in range(n_layers)]
+    vcache = [torch.empty(max(slice_rows, 1) * NKV * row, dtype=torch.uint8, device="cuda") for _ in range(n_layers)]
+    for l in range(n_layers):
+        rd.check(L.rd_kv_fill(KT, rd.ptr(kcache[l]), slice_rows * NKV, HD, 11 + 100 * l + rank, st))
+        rd.check(L.rd_kv_fill(VT, rd.ptr(vcache[l]), slice_rows * NKV, HD, 22 + 100 * l + rank, st))
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q_host = torch.randn(n_layers, NH, HD, generator=g).pin_memory()
+    gate_host = torch.randn(n_layers, NH, HD, generator=g).pin_memory()
+    knew_host = torch.randn(n_layers, NKV, HD, generator=g).pin_memory()
+    vnew_host = torch.randn(n_layers, NKV, HD, generator=g).pin_memory()
+    out_host = torch.empty(n_layers, NH, HD).pin_memory()
+    q_dev, gate_dev = q_host.cuda(), gate_host.cuda()
+    knew_dev, vnew_dev = knew_host.cuda(), vnew_host.cuda()
+    ws_bytes = L.rd_attn_workspace_bytes(1, NH, HD)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    rec_mine = torch.empty(NH, 1, 2 + HD, device="cuda")
+    rec_all = torch.empty(world, NH, 1, 2 + HD, device="cuda")
+    rec_merge = torch.empty(NH, world, 2 + HD, device="cuda")
+
+    o_dev = torch.empty_like(q_dev)
+
+    def layer_step(l, host_io):
+        st = rd.stream_ptr()   # the capturing stream while a graph is being recorded
+        if host_io:
+            q_dev[l].copy_(q_host[l], non_blocking=True)
+            gate_dev[l].copy_(gate_host[l], non_blocking=True)
+            knew_dev[l].copy_(knew_host[l], non_blocking=True)
+            vnew_dev[l].copy_(vnew_host[l], non_blocking=True)
+        n = 0
+        if owns_new_row:
+            off = (POS - kb) * NKV * row
+            rd.check(L.rd_kv_append(KT, VT, rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
+                                    rd.ptr(kcache[l]) + off, rd.ptr(vcache[l]) + off, 1, NKV, HD, None, 0,
+                                    0.0, st))
+            n += 1
+        if world == 1:
+            rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]),
+                                         rd.ptr(o_dev[l]), None, 0, POS, NH, NKV, HD, SCALE, KT, VT, 16,
+                                         rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes, st))
+            n += 2
+        else:
+            rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
+                                         rd.ptr(rec_mine), 0, slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, 1,
+                                         None, rd.ptr(ws), ws_bytes, st))
+            dist.all_gather_into_tensor(rec_all, rec_mine)
+            rec_merge.copy_(rec_all.view(world, NH, 2 + HD).transpose(0, 1))
+            rd.check(L.rd_attn_merge(rd.ptr(rec_merge), rd.ptr(o_dev[l]), NH, HD, world,
+                                     rd.ptr(gate_dev[l]), st))
+            n += 3
+        if host_io:
+            out_host[l].copy_(o_dev[l], non_blocking=True)
+        return n
+
+    def one_step(host_io):
+        return sum(layer_step(l, host_io) for l in range(n_layers))
+
+    # One step (16 layers) is recorded into a CUDA graph and replayed: the per-launch
+    # host cost of a Python caller would otherwise hide a ~30 us kernel. The device-
+    # resident graph keeps q/gate/new rows in HBM; the end-to-end graph also holds the
+    # pinned-host copies in and the result copy out.
+    def make_graph(host_io):
+        for _ in range(3):
+            one_step(host_io)        # eager warm-up: first-call attribute set-up, NCCL
+        torch.cuda.synchronize()
+        try:
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph):
+                n = one_step(host_io)
+            return gph, n
+        except Exception as e:  # fall back to eager launches (keeps the bench alive)
+            if rank == 0:
+                print(f"# graph capture failed ({e}); running eagerly", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None, one_step(host_io)
+
+    def timed(gph, n, host_io):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            if gph is not None:
+                gph.replay()
+            else:
+                one_step(host_io)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    g_dev, per_step = make_graph(False)
+    g_e2e, _ = make_graph(True)
+    timed(g_dev, W, False)
+    sampler.start()
+    ms_dev = timed(g_dev, K, False)
+    n_launch = per_step * K
+    timed(g_e2e, min(W, 3), True)
+    ms_e2e = timed(g_e2e, K, True)
+    clocks = sampler.stop()
+    rd.check(L.rd_device_status(), "device status")
+    st = rd.stream_ptr()
+
+    bytes_layer = algorithmic_bytes(N_KEYS, row, row)
+    bytes_step = bytes_layer * n_layers
+    value = bytes_step * K / (ms_dev * 1e-3) / 1e9
+    e2e = bytes_step * K / (ms_e2e * 1e-3) / 1e9
+
+    # ---- roofline of the decode kernel alone (rank 0's slice, records-only launches) --
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+    sms = torch.cuda.get_device_properties(local).multi_processor_count
+    tile = 32
+    n_rec = min(sms, (slice_rows + tile - 1) // tile)
+    rec = torch.empty(NH, n_rec, 2 + HD, device="cuda")
+    reps = 20 * n_layers
+
+    def kernel_only(n):
+        for i in range(n):
+            l = i % n_layers
+            rd.check(L.rd_attn_decode_split(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
+                                            rd.ptr(rec), slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, n_rec, st))
+    kernel_only(n_layers)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    kernel_only(reps)
+    e1.record()
+    torch.cuda.synchronize()
+    k_ms = e0.elapsed_time(e1) / reps
+    k_bytes = algorithmic_bytes(slice_rows, row, row)
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    traffic = None
+    try:
+        prof = json.load(open(os.path.join(ROOT, "profiles", "decode_q4_0_traffic.json")))
+        traffic = prof["dram_bytes_per_key"] * slice_rows
+    except Exception:
+        pass
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "kernel": "decode_kernel<q4_0,q4_0>", "kernel_us": k_ms * 1e3,
+                "peak_source": peak_src, "frac_of_8tbs_nominal": achieved / 8000.0}
+
+    out = {
+        "metric": "decode_attn_hbm_gbs_128k_q4_0", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms_dev / K, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": value / 63.0, "dtype": "f16 mma / f32 softmax+accumulate",
+        "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e / K,
+                "h2d_bytes_per_step": n_layers * (2 * NH * HD * 4 + 2 * NKV * HD * 4),
+                "d2h_bytes_per_step": n_layers * NH * HD * 4},
+        "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
+        "us_per_layer": ms_dev / K / n_layers * 1e3,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle.oracle import Oracle
+        ora = Oracle()
+        kc = kcache[0].cpu().numpy()
+        vc = vcache[0].cpu().numpy()
+        qn = q_host[0].numpy()
+        t0 = time.perf_counter()
+        ora.attn(qn[None], kc, vc, [POS], NKV, SCALE, KT, VT)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": bytes_layer / dt / 1e9, "unit": "GB/s", "cores": ora.num_threads(),
+                               "kind": "port", "sample": "one layer-step (131001 keys) of the same workload, "
+                               "CPU oracle f32 attention, OpenMP over heads", "seconds": dt}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,178 @@
+/*
+ * rd_attn.h -- C ABI of the B200 (sm_100a) attention / KV-cache library.
+ *
+ * This is the drop-in boundary for the attention hot path of rdna4-infer: every
+ * entry point below replaces one launcher of the reference's
+ * include/rdna4/{kv.h,attn.cuh,attn_fa2.cuh,nn.cuh,gdn.cuh} (cited per function,
+ * paths relative to the reference project). The C++17 wrappers in
+ * include/rdna4/ give the same names and signatures as the reference in
+ * namespace rdna4 and forward here.
+ *
+ * Conventions kept from the reference:
+ *   - all pointers are caller-owned DEVICE pointers unless a comment says host;
+ *   - activations are f32; q and out may be the same buffer;
+ *   - K/V caches are rows [key][n_head_kv] of `row_bytes(type, head_dim)` bytes in
+ *     GGUF 32-element blocks (fp16 scale first), key j / kv head h at
+ *     (j*n_head_kv + h) * row_bytes;
+ *   - `t` is the index of the LAST attended key (n_keys = t + 1); `pos[]` is a device
+ *     int32 array with one such index per query token;
+ *   - `scale` is passed in, never recomputed; `stream` is a cudaStream_t (NULL = the
+ *     default stream); launch order on the stream is the only synchronisation;
+ *   - no host synchronisation and no allocation inside a call, with one documented
+ *     exception: the launchers that keep the reference's small `partial` argument
+ *     (rd_attn_decode, rd_attn_decode_split, rd_attn_batch, rd_attn_split_batch) grow
+ *     a per-device workspace with cudaMalloc the first time a shape needs it, because
+ *     148 SMs want more partial records than the reference's 16-split buffer holds.
+ *     The *_ws entry points take the workspace from the caller and never allocate.
+ *
+ * Every function returns RD_OK (0) or a negative RD_ERR_* code; nothing aborts and
+ * nothing traps on the device. Shapes outside the supported set are refused with
+ * RD_ERR_UNSUPPORTED: head_dim must be 256, n_head == 6 * n_head_kv, n_head_kv in
+ * {1, 2, 4}; K/V types f32, f16, q8_0, q4_0 for attention (q5_0 / q4_1 are stored and
+ * filled but not yet attended).
+ */
+#ifndef RD_ATTN_H
+#define RD_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* KvType of include/rdna4/kv.h:89-98 (values never renumbered). */
+enum {
+  RD_KV_F32 = 0,
+  RD_KV_F16 = 1,
+  RD_KV_Q8_0 = 2,
+  RD_KV_Q4_0 = 3,
+  RD_KV_Q5_0 = 4,
+  RD_KV_Q4_1 = 5
+};
+
+enum {
+  RD_OK = 0,
+  RD_ERR_TYPE = -1,        /* KV type outside the enum */
+  RD_ERR_SHAPE = -2,       /* negative / zero / non-multiple-of-32 sizes, n_splits < 1 ... */
+  RD_ERR_UNSUPPORTED = -3, /* valid for the reference, not built here (see above) */
+  RD_ERR_NULL = -4,        /* a required pointer is NULL */
+  RD_ERR_ALIGN = -5,       /* a pointer is not aligned as the entry point requires */
+  RD_ERR_CUDA = -6,        /* a CUDA runtime call or launch failed */
+  RD_ERR_WORKSPACE = -7,   /* caller-provided workspace too small / workspace growth failed */
+  RD_ERR_DEVICE = -8       /* a kernel recorded a bounded-wait timeout (rd_device_status) */
+};
+
+const char *rd_strerror(int code);
+
+/* ---- KV tables: kv_type_name / kv_type_parse / kv_bytes_per_elem / kv_row_bytes,
+ * include/rdna4/kv.h:100-169. Unknown types return NULL / 0 here; the C++ wrapper
+ * aborts on them as the reference does (kv.h:58-69). */
+const char *rd_kv_type_name(int type);
+int rd_kv_type_parse(const char *name, int *out_type);
+double rd_kv_bytes_per_elem(int type);
+uint64_t rd_kv_row_bytes(int type, int head_dim);
+
+/* ---- KV append: kv_store_row_launch(t, src, dst, width), include/rdna4/kv.h:673-694.
+ * `width` consecutive f32 values (n_tok * n_head_kv * head_dim, graph.cuh:1028) are
+ * stored as width/32 blocks (or width scalars). Bit-exact with the reference
+ * quantizers for all six types. src 4-byte, dst 2-byte aligned. */
+int rd_kv_store_rows(int type, const float *src, void *dst, int64_t width, void *stream);
+
+/* One launch for the K and the V rows of a chunk (the two calls of
+ * Graph::kv_write_batch, graph.cuh:1011-1035), optionally applying RoPE to the K rows
+ * first (pos != NULL): k_src is then [n_tok][n_head_kv][head_dim] and is NOT
+ * modified. Without RoPE this is exactly two rd_kv_store_rows. */
+int rd_kv_append(int k_type, int v_type, const float *k_src, const float *v_src, void *k_dst,
+                 void *v_dst, int n_tok, int n_head_kv, int head_dim, const int32_t *pos,
+                 int n_rot, float freq_base, void *stream);
+
+/* ---- synthetic cache: kv_fill_launch, include/rdna4/kv.h:632-671. Row r, element e
+ * holds kv_rand(r*head_dim+e, seed) stored with the real quantizer (the reference's
+ * own q4_0 fill writes racing per-byte scales and is not reproduced). */
+int rd_kv_fill(int type, void *cache, int64_t n_rows, int head_dim, uint32_t seed, void *stream);
+
+/* ---- RoPE: rope_launch, include/rdna4/attn.cuh:56-63. In place on
+ * x[n_tok][n_heads][head_dim], split-half pairs of the first n_rot dims. */
+int rd_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float freq_base,
+            const int32_t *pos, void *stream);
+
+/* ---- gate glue: deinterleave_q_gate(_batch)_launch, include/rdna4/gdn.cuh:377-384,
+ * 853-862, and sigmoid_gate_launch, include/rdna4/nn.cuh:414-420 (y *= sigmoid(g),
+ * sigmoid stored back into g). */
+int rd_deinterleave_q_gate(const float *yq, float *q, float *gate, int n_tok, int n_head,
+                           int head_dim, void *stream);
+int rd_sigmoid_gate(float *g_io, float *y_io, int64_t n, void *stream);
+
+/* ---- partial records: attn_partial_bytes, include/rdna4/attn.cuh:665-667.
+ * A record is (m, l, acc[head_dim]) f32 in natural-log units: m = max scaled score,
+ * l = sum exp(s - m), acc = sum exp(s - m) * v; an empty record is (-inf, 0, 0...). */
+size_t rd_attn_partial_bytes(int n_head, int head_dim, int n_splits);
+
+/* Workspace the decode kernels want for `n_tok` query tokens on the current device
+ * (internal split records + status word). Pass it to the *_ws entry points. */
+size_t rd_attn_workspace_bytes(int n_tok, int n_head, int head_dim);
+
+/* ---- single-token attention: attn_launch, include/rdna4/attn.cuh:201-249. */
+int rd_attn_decode(const float *q, const void *k, const void *v, float *out, int t, int n_head,
+                   int n_head_kv, int head_dim, float scale, int k_type, int v_type,
+                   void *stream);
+
+/* ---- split-KV single-token attention: attn_launch_split, include/rdna4/attn.cuh:903-956.
+ * `n_splits` is a hint: the kernel spreads the keys over all SMs and merges. If
+ * `out` is NULL, `partial` receives exactly n_splits records per head in the
+ * reference layout [h][s][2+head_dim] (split s owns the s-th contiguous slice of the
+ * keys) and no merge runs; otherwise `partial` may be NULL. */
+int rd_attn_decode_split(const float *q, const void *k, const void *v, float *out,
+                         float *partial, int t, int n_head, int n_head_kv, int head_dim,
+                         float scale, int k_type, int v_type, int n_splits, void *stream);
+
+/* The same with every option spelled out and no allocation:
+ *   key_begin..t     the attended key range (key_begin > t gives the empty record);
+ *   gate             optional [n_head][head_dim]: out *= sigmoid(gate) fused into the
+ *                    merge, sigmoid stored back (nn.cuh:405-412);
+ *   workspace/bytes  from rd_attn_workspace_bytes(1, ...), 256-byte aligned. */
+int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, float *partial,
+                      int key_begin, int t, int n_head, int n_head_kv, int head_dim, float scale,
+                      int k_type, int v_type, int n_splits, float *gate, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
+/* ---- merge: attn_merge_kernel / attn_merge_batch_kernel launches,
+ * include/rdna4/attn.cuh:563-590,795-827. partial [n_rows][n_splits][2+head_dim],
+ * out [n_rows][head_dim] with n_rows = n_tok * n_head. Rows whose records are all
+ * empty give zeros. `gate` as above (may be NULL). */
+int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,
+                  float *gate, void *stream);
+
+/* ---- multi-token attention (prefill chunk, speculative verify): attn_batch_launch,
+ * include/rdna4/attn.cuh:373-424, and attn_split_batch_launch, :958-1049. Token i
+ * attends keys 0..pos[i]. q/out [n_tok][n_head][head_dim]. */
+int rd_attn_batch(const float *q, const void *k, const void *v, float *out, const int32_t *pos,
+                  int n_tok, int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                  int v_type, void *stream);
+int rd_attn_split_batch(const float *q, const void *k, const void *v, float *out, float *partial,
+                        const int32_t *pos, int n_tok, int n_head, int n_head_kv, int head_dim,
+                        float scale, int k_type, int v_type, int n_splits, void *stream);
+
+/* ---- causal prefill tile kernel: fa2_prefill_usable / fa2_prefill_launch,
+ * include/rdna4/attn_fa2.cuh:174-207. f16/f16 caches. The admission window is wider
+ * than the reference's (any n_q >= 1 and any key count), since the tensor-core
+ * kernel has no measured-only range to protect. */
+int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head, int n_head_kv,
+                          int head_dim);
+int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
+                   int n_q, int kmax, int keys_total, int n_head, int n_head_kv, int head_dim,
+                   float scale, void *stream);
+
+/* ---- device status: 0, or RD_ERR_DEVICE if any kernel launched through this
+ * library on the current device gave up on a bounded wait since the last call.
+ * Synchronises the device; meant for tests and debugging, not for the hot path. */
+int rd_device_status(void);
+
+/* Library identification ("rd_attn_b200 <version> sm_100a"). */
+const char *rd_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RD_ATTN_H */

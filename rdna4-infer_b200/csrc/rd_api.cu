@@ -1,0 +1,406 @@
+// extern "C" entry points: argument validation, split planning, per-device workspace.
+#include <mutex>
+#include <string.h>
+
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace {
+
+using namespace rd;
+
+constexpr int kMaxDevices = 32;
+
+struct DeviceState {
+  int sms = 0;
+  DeviceStatus *status = nullptr;  // sticky status word
+  void *ws = nullptr;              // grown on demand by the allocating entry points
+  size_t ws_bytes = 0;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+
+int current_device(int *dev) {
+  if (cudaGetDevice(dev) != cudaSuccess) return RD_ERR_CUDA;
+  if (*dev < 0 || *dev >= kMaxDevices) return RD_ERR_UNSUPPORTED;
+  return RD_OK;
+}
+
+int sm_count(int dev) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_dev[dev].sms == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    g_dev[dev].sms = n;
+  }
+  return g_dev[dev].sms;
+}
+
+// Lazily allocated status word (only the allocating entry points create it).
+DeviceStatus *status_word(int dev, bool create) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_dev[dev].status == nullptr && create) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, 256) == cudaSuccess && cudaMemset(p, 0, 256) == cudaSuccess)
+      g_dev[dev].status = (DeviceStatus *)p;
+  }
+  return g_dev[dev].status;
+}
+
+void *ensure_workspace(int dev, size_t bytes) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState &d = g_dev[dev];
+  if (d.ws_bytes >= bytes) return d.ws;
+  if (d.ws != nullptr) cudaFree(d.ws);  // synchronises with work still using it
+  d.ws = nullptr;
+  d.ws_bytes = 0;
+  const size_t want = (bytes + (size_t)(1 << 20) - 1) & ~(size_t)((1 << 20) - 1);
+  if (cudaMalloc(&d.ws, want) != cudaSuccess) {
+    d.ws = nullptr;
+    return nullptr;
+  }
+  d.ws_bytes = want;
+  return d.ws;
+}
+
+bool known_type(int t) { return t >= RD_KV_F32 && t <= RD_KV_Q4_1; }
+bool aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+// Shape gate shared by every attention entry point.
+int check_attn_shape(int n_head, int n_head_kv, int head_dim, int kt, int vt) {
+  if (!known_type(kt) || !known_type(vt)) return RD_ERR_TYPE;
+  if (head_dim <= 0 || head_dim % 32 != 0 || head_dim > 512) return RD_ERR_SHAPE;
+  if (n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv != 0) return RD_ERR_SHAPE;
+  if (head_dim != kHeadDim || n_head / n_head_kv != kGroup) return RD_ERR_UNSUPPORTED;
+  if (n_head_kv != 1 && n_head_kv != 2 && n_head_kv != 4) return RD_ERR_UNSUPPORTED;
+  if (kt > RD_KV_Q4_0 || vt > RD_KV_Q4_0) return RD_ERR_UNSUPPORTED;
+  return RD_OK;
+}
+
+// Internal split count: about one CTA per SM over the whole launch, never more
+// splits than key tiles (when the key count is known on the host).
+int plan_splits(int sms, int n_tok, int64_t tiles_known) {
+  int s = sms / (n_tok > 0 ? n_tok : 1);
+  if (s < 1) s = 1;
+  if (tiles_known >= 0 && s > tiles_known) s = tiles_known > 0 ? (int)tiles_known : 1;
+  return s;
+}
+
+size_t partial_floats(int n_tok, int n_head, int splits) {
+  return (size_t)n_tok * n_head * splits * kRec;
+}
+
+// Core: attention of n_tok tokens over keys key_begin..(pos ? pos[i] : t).
+//   out != null: merged (and optionally gated) output;
+//   out == null: exactly n_rec records per (token, head) into `records`.
+int attn_core(const float *q, const void *k, const void *v, float *out, float *records, int n_rec,
+              const int32_t *pos, int t, int key_begin, int n_tok, int n_head, int n_head_kv,
+              float scale, int kt, int vt, float *gate, void *ws, size_t ws_bytes,
+              DeviceStatus *status, int sms, cudaStream_t st) {
+  const int tile = decode_tile_keys(kt, vt);
+  int64_t tiles = -1;
+  if (pos == nullptr) {
+    const int64_t n_keys = t >= key_begin ? (int64_t)t - key_begin + 1 : 0;
+    tiles = (n_keys + tile - 1) / tile;
+  }
+  int S = plan_splits(sms, n_tok, tiles);
+  if (out == nullptr) {
+    // nest the internal splits inside the caller's: S = n_rec * r
+    int r = S / n_rec;
+    if (r < 1) r = 1;
+    S = n_rec * r;
+  }
+  DecodeArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.pos = pos;
+  a.t = t;
+  a.key_begin = key_begin;
+  a.n_tok = n_tok;
+  a.n_head = n_head;
+  a.n_head_kv = n_head_kv;
+  a.scale = scale;
+  a.n_splits = S;
+  a.status = status;
+  if (out == nullptr && S == n_rec) {
+    a.partial = records;
+    return launch_decode(kt, vt, a, st);
+  }
+  const size_t need = partial_floats(n_tok, n_head, S) * sizeof(float);
+  if (ws == nullptr || ws_bytes < need) return RD_ERR_WORKSPACE;
+  a.partial = (float *)ws;
+  int rc = launch_decode(kt, vt, a, st);
+  if (rc != RD_OK) return rc;
+  if (out != nullptr) return launch_merge((const float *)ws, out, n_tok * n_head, S, gate, st);
+  return launch_merge_records((const float *)ws, records, n_tok * n_head, S, n_rec, st);
+}
+
+size_t workspace_bytes_for(int sms, int n_tok, int n_head) {
+  // the largest split count attn_core can pick for this token count, plus slack for
+  // the "nest inside the caller's splits" rounding
+  const int s = plan_splits(sms, n_tok, -1);
+  return partial_floats(n_tok, n_head, s) * sizeof(float) + 256;
+}
+
+// Allocating flavour used by the reference-shaped launchers.
+int attn_alloc(const float *q, const void *k, const void *v, float *out, float *records, int n_rec,
+               const int32_t *pos, int t, int n_tok, int n_head, int n_head_kv, int head_dim,
+               float scale, int kt, int vt, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, kt, vt);
+  if (rc != RD_OK) return rc;
+  if (q == nullptr || k == nullptr || v == nullptr) return RD_ERR_NULL;
+  if (out == nullptr && records == nullptr) return RD_ERR_NULL;
+  if (n_tok < 1 || n_rec < 1) return RD_ERR_SHAPE;
+  if (!aligned(q, 4) || !aligned(out, 4) || !aligned(records, 4)) return RD_ERR_ALIGN;
+  if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  const int sms = sm_count(dev);
+  size_t bytes = workspace_bytes_for(sms, n_tok, n_head);
+  if (out == nullptr) {
+    const size_t nested = partial_floats(n_tok, n_head, sms + n_rec) * sizeof(float);
+    if (nested > bytes) bytes = nested;
+  }
+  void *ws = ensure_workspace(dev, bytes);
+  if (ws == nullptr) return RD_ERR_WORKSPACE;
+  return attn_core(q, k, v, out, records, n_rec, pos, t, 0, n_tok, n_head, n_head_kv, scale, kt, vt,
+                   nullptr, ws, bytes, status_word(dev, true), sms, (cudaStream_t)stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *rd_version(void) { return "rd_attn_b200 0.1 sm_100a"; }
+
+const char *rd_strerror(int code) {
+  switch (code) {
+    case RD_OK: return "ok";
+    case RD_ERR_TYPE: return "KV type outside the enum";
+    case RD_ERR_SHAPE: return "bad shape or size";
+    case RD_ERR_UNSUPPORTED: return "shape or type not built in this library";
+    case RD_ERR_NULL: return "required pointer is NULL";
+    case RD_ERR_ALIGN: return "pointer not aligned as required";
+    case RD_ERR_CUDA: return "CUDA runtime error";
+    case RD_ERR_WORKSPACE: return "workspace missing or too small";
+    case RD_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+  }
+  return "unknown error code";
+}
+
+const char *rd_kv_type_name(int type) {
+  static const char *names[] = {"f32", "f16", "q8_0", "q4_0", "q5_0", "q4_1"};
+  return known_type(type) ? names[type] : nullptr;
+}
+
+int rd_kv_type_parse(const char *name, int *out_type) {
+  if (name == nullptr || out_type == nullptr) return RD_ERR_NULL;
+  for (int t = RD_KV_F32; t <= RD_KV_Q4_1; ++t) {
+    if (strcmp(name, rd_kv_type_name(t)) == 0) {
+      *out_type = t;
+      return RD_OK;
+    }
+  }
+  return RD_ERR_TYPE;
+}
+
+double rd_kv_bytes_per_elem(int type) {
+  switch (type) {
+    case RD_KV_F32: return 4.0;
+    case RD_KV_F16: return 2.0;
+    case RD_KV_Q8_0: return 34.0 / 32.0;
+    case RD_KV_Q4_0: return 18.0 / 32.0;
+    case RD_KV_Q5_0: return 22.0 / 32.0;
+    case RD_KV_Q4_1: return 20.0 / 32.0;
+  }
+  return 0.0;
+}
+
+uint64_t rd_kv_row_bytes(int type, int head_dim) {
+  if (head_dim < 0) return 0;
+  const uint64_t blocks = (uint64_t)(head_dim + 31) / 32;
+  switch (type) {
+    case RD_KV_F32: return (uint64_t)head_dim * 4;
+    case RD_KV_F16: return (uint64_t)head_dim * 2;
+    case RD_KV_Q8_0: return blocks * 34;
+    case RD_KV_Q4_0: return blocks * 18;
+    case RD_KV_Q5_0: return blocks * 22;
+    case RD_KV_Q4_1: return blocks * 20;
+  }
+  return 0;
+}
+
+int rd_kv_store_rows(int type, const float *src, void *dst, int64_t width, void *stream) {
+  if (!known_type(type)) return RD_ERR_TYPE;
+  if (width < 0 || width % 32 != 0) return RD_ERR_SHAPE;
+  if (width == 0) return RD_OK;
+  if (src == nullptr || dst == nullptr) return RD_ERR_NULL;
+  if (!aligned(src, 4) || !aligned(dst, type == RD_KV_F32 ? 4 : 2)) return RD_ERR_ALIGN;
+  return launch_kv_append(type, type, src, nullptr, dst, nullptr, width, kHeadDim, 1, nullptr, 0,
+                          0.f, (cudaStream_t)stream);
+}
+
+int rd_kv_append(int k_type, int v_type, const float *k_src, const float *v_src, void *k_dst,
+                 void *v_dst, int n_tok, int n_head_kv, int head_dim, const int32_t *pos, int n_rot,
+                 float freq_base, void *stream) {
+  if (!known_type(k_type) || !known_type(v_type)) return RD_ERR_TYPE;
+  if (n_tok < 0 || n_head_kv < 1 || head_dim < 32 || head_dim % 32 != 0) return RD_ERR_SHAPE;
+  if (pos != nullptr && (n_rot < 2 || n_rot % 2 != 0 || n_rot > head_dim)) return RD_ERR_SHAPE;
+  if (n_tok == 0) return RD_OK;
+  if (k_src == nullptr || v_src == nullptr || k_dst == nullptr || v_dst == nullptr)
+    return RD_ERR_NULL;
+  if (!aligned(k_src, 4) || !aligned(v_src, 4) || !aligned(k_dst, k_type == RD_KV_F32 ? 4 : 2) ||
+      !aligned(v_dst, v_type == RD_KV_F32 ? 4 : 2))
+    return RD_ERR_ALIGN;
+  const int64_t width = (int64_t)n_tok * n_head_kv * head_dim;
+  return launch_kv_append(k_type, v_type, k_src, v_src, k_dst, v_dst, width, head_dim, n_head_kv,
+                          pos, n_rot, freq_base, (cudaStream_t)stream);
+}
+
+int rd_kv_fill(int type, void *cache, int64_t n_rows, int head_dim, uint32_t seed, void *stream) {
+  if (!known_type(type)) return RD_ERR_TYPE;
+  if (n_rows < 0 || head_dim < 32 || head_dim % 32 != 0) return RD_ERR_SHAPE;
+  if (n_rows == 0) return RD_OK;
+  if (cache == nullptr) return RD_ERR_NULL;
+  if (!aligned(cache, type == RD_KV_F32 ? 4 : 2)) return RD_ERR_ALIGN;
+  return launch_kv_fill(type, cache, n_rows, head_dim, seed, (cudaStream_t)stream);
+}
+
+int rd_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float freq_base,
+            const int32_t *pos, void *stream) {
+  if (n_tok < 0 || n_heads < 1 || head_dim < 2 || n_rot < 2 || n_rot % 2 != 0 || n_rot > head_dim)
+    return RD_ERR_SHAPE;
+  if (n_tok == 0) return RD_OK;
+  if (x == nullptr || pos == nullptr) return RD_ERR_NULL;
+  if (!aligned(x, 4) || !aligned(pos, 4)) return RD_ERR_ALIGN;
+  return launch_rope(x, n_tok, n_heads, head_dim, n_rot, freq_base, pos, (cudaStream_t)stream);
+}
+
+int rd_deinterleave_q_gate(const float *yq, float *q, float *gate, int n_tok, int n_head,
+                           int head_dim, void *stream) {
+  if (n_tok < 0 || n_head < 1 || head_dim < 4 || head_dim % 4 != 0) return RD_ERR_SHAPE;
+  if (n_tok == 0) return RD_OK;
+  if (yq == nullptr || q == nullptr || gate == nullptr) return RD_ERR_NULL;
+  if (!aligned(yq, 16) || !aligned(q, 16) || !aligned(gate, 16)) return RD_ERR_ALIGN;
+  return launch_deinterleave(yq, q, gate, (int64_t)n_tok * n_head, head_dim, (cudaStream_t)stream);
+}
+
+int rd_sigmoid_gate(float *g_io, float *y_io, int64_t n, void *stream) {
+  if (n < 0) return RD_ERR_SHAPE;
+  if (n == 0) return RD_OK;
+  if (g_io == nullptr || y_io == nullptr) return RD_ERR_NULL;
+  return launch_sigmoid_gate(g_io, y_io, n, (cudaStream_t)stream);
+}
+
+size_t rd_attn_partial_bytes(int n_head, int head_dim, int n_splits) {
+  if (n_head < 0 || head_dim < 0 || n_splits < 0) return 0;
+  return (size_t)n_head * (size_t)n_splits * (2 + (size_t)head_dim) * sizeof(float);
+}
+
+size_t rd_attn_workspace_bytes(int n_tok, int n_head, int head_dim) {
+  int dev;
+  if (n_tok < 1 || n_head < 1 || head_dim != kHeadDim || current_device(&dev) != RD_OK) return 0;
+  const int sms = sm_count(dev);
+  // room for the largest nested split count as well (records-only calls)
+  return partial_floats(n_tok, n_head, 2 * sms) * sizeof(float) + 256;
+}
+
+int rd_attn_decode(const float *q, const void *k, const void *v, float *out, int t, int n_head,
+                   int n_head_kv, int head_dim, float scale, int k_type, int v_type,
+                   void *stream) {
+  if (out == nullptr) return RD_ERR_NULL;
+  return attn_alloc(q, k, v, out, nullptr, 1, nullptr, t, 1, n_head, n_head_kv, head_dim, scale,
+                    k_type, v_type, stream);
+}
+
+int rd_attn_decode_split(const float *q, const void *k, const void *v, float *out, float *partial,
+                         int t, int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                         int v_type, int n_splits, void *stream) {
+  if (n_splits < 1) return RD_ERR_SHAPE;
+  return attn_alloc(q, k, v, out, partial, n_splits, nullptr, t, 1, n_head, n_head_kv, head_dim,
+                    scale, k_type, v_type, stream);
+}
+
+int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, float *partial,
+                      int key_begin, int t, int n_head, int n_head_kv, int head_dim, float scale,
+                      int k_type, int v_type, int n_splits, float *gate, void *workspace,
+                      size_t workspace_bytes, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (n_splits < 1 || key_begin < 0) return RD_ERR_SHAPE;
+  if (q == nullptr || k == nullptr || v == nullptr) return RD_ERR_NULL;
+  if (out == nullptr && partial == nullptr) return RD_ERR_NULL;
+  if (workspace == nullptr) return RD_ERR_WORKSPACE;
+  if (!aligned(q, 4) || !aligned(out, 4) || !aligned(partial, 4) || !aligned(gate, 4))
+    return RD_ERR_ALIGN;
+  if (!aligned(k, 16) || !aligned(v, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  return attn_core(q, k, v, out, partial, n_splits, nullptr, t, key_begin, 1, n_head, n_head_kv,
+                   scale, k_type, v_type, gate, workspace, workspace_bytes, status_word(dev, false),
+                   sm_count(dev), (cudaStream_t)stream);
+}
+
+int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,
+                  float *gate, void *stream) {
+  if (n_rows < 0 || n_splits < 1) return RD_ERR_SHAPE;
+  if (head_dim != kHeadDim) return head_dim > 0 && head_dim % 32 == 0 ? RD_ERR_UNSUPPORTED
+                                                                      : RD_ERR_SHAPE;
+  if (n_rows == 0) return RD_OK;
+  if (partial == nullptr || out == nullptr) return RD_ERR_NULL;
+  if (!aligned(partial, 4) || !aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
+  return launch_merge(partial, out, n_rows, n_splits, gate, (cudaStream_t)stream);
+}
+
+int rd_attn_batch(const float *q, const void *k, const void *v, float *out, const int32_t *pos,
+                  int n_tok, int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                  int v_type, void *stream) {
+  if (out == nullptr || pos == nullptr) return RD_ERR_NULL;
+  return attn_alloc(q, k, v, out, nullptr, 1, pos, 0, n_tok, n_head, n_head_kv, head_dim, scale,
+                    k_type, v_type, stream);
+}
+
+int rd_attn_split_batch(const float *q, const void *k, const void *v, float *out, float *partial,
+                        const int32_t *pos, int n_tok, int n_head, int n_head_kv, int head_dim,
+                        float scale, int k_type, int v_type, int n_splits, void *stream) {
+  if (n_splits < 1 || n_tok < 1) return RD_ERR_SHAPE;
+  if (pos == nullptr) return RD_ERR_NULL;
+  return attn_alloc(q, k, v, out, partial, n_splits, pos, 0, n_tok, n_head, n_head_kv, head_dim,
+                    scale, k_type, v_type, stream);
+}
+
+int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head, int n_head_kv,
+                          int head_dim) {
+  if (k_type != RD_KV_F16 || v_type != RD_KV_F16) return 0;
+  if (n_q < 1 || pos0 < 0) return 0;
+  return check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type) == RD_OK ? 1 : 0;
+}
+
+int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
+                   int n_q, int kmax, int keys_total, int n_head, int n_head_kv, int head_dim,
+                   float scale, void *stream) {
+  if (n_q < 1 || kmax < 0 || keys_total <= 0) return RD_ERR_SHAPE;
+  if (o == nullptr || pos == nullptr) return RD_ERR_NULL;
+  return attn_alloc(q, k, v, o, nullptr, 1, pos, 0, n_q, n_head, n_head_kv, head_dim, scale,
+                    RD_KV_F16, RD_KV_F16, stream);
+}
+
+int rd_device_status(void) {
+  int dev;
+  int rc = current_device(&dev);
+  if (rc != RD_OK) return rc;
+  DeviceStatus *st = status_word(dev, true);
+  if (st == nullptr) return RD_ERR_CUDA;
+  if (cudaDeviceSynchronize() != cudaSuccess) return RD_ERR_CUDA;
+  DeviceStatus h;
+  if (cudaMemcpy(&h, st, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return RD_ERR_CUDA;
+  if (h.timeout_flag != 0) {
+    cudaMemset(st, 0, sizeof(h));
+    return RD_ERR_DEVICE;
+  }
+  return RD_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+// Shared device/host helpers of the sm_100a attention / KV-cache library.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rd_attn.h"
+
+namespace rd {
+
+constexpr int kHeadDim = 256;   // the only head size built (reference model: qwen35)
+constexpr int kGroup = 6;       // query heads per KV head
+constexpr int kRec = 2 + kHeadDim;  // floats in one partial record (m, l, acc[256])
+
+// Bytes of one stored row of kHeadDim elements; include/rdna4/kv.h:155-169.
+__host__ __device__ constexpr int row_bytes(int type) {
+  return type == RD_KV_F32   ? kHeadDim * 4
+         : type == RD_KV_F16 ? kHeadDim * 2
+         : type == RD_KV_Q8_0 ? 8 * 34
+         : type == RD_KV_Q4_0 ? 8 * 18
+         : type == RD_KV_Q5_0 ? 8 * 22
+         : type == RD_KV_Q4_1 ? 8 * 20
+                              : 0;
+}
+
+// Status word written by kernels that give up on a bounded wait. Lives at the start
+// of the workspace; sticky until read by rd_device_status().
+struct DeviceStatus {
+  int timeout_flag;   // non-zero: some wait ran out
+  int where;          // site id of the first wait that ran out
+  int pad[2];
+};
+
+// ---- decode tile geometry (shared by the kernel and the host-side split planning)
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 220 * 1024;  // per CTA, of the 227 KB an sm_100 CTA may use
+
+// Bytes of one key in a shared-memory tile: the n_head_kv rows plus 16 bytes, which
+// makes the per-lane row walks of every loader above bank-conflict-free for
+// n_head_kv == 4 (pitch = 16 or 80 bytes mod 128).
+__host__ __device__ constexpr int key_pitch(int type, int nkv) { return nkv * row_bytes(type) + 16; }
+
+// 16-key groups per tile: 2 when three 32-key stages fit the budget, else 1.
+__host__ __device__ constexpr int key_groups(int kt, int vt) {
+  return 3 * 32 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget ? 2 : 1;
+}
+
+// ---- PTX helpers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// (a & b) | c in one LOP3 (immLut 0xEA).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+// half2 fma on raw 32-bit registers.
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// D = A(16x16, row) * B(16x8, col) + D, f16 inputs, f32 accumulate.
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Warp-wide transpose of an 8x8 matrix of b16 held in mma fragment layout.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
+  return r;
+}
+
+// ---- mbarrier / bulk copy ------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kWaitLimit polls, records the site in `status` and
+// returns false so the caller can unwind without leaving the GPU spinning.
+constexpr uint32_t kWaitLimit = 4u << 20;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, DeviceStatus *status,
+                                          int site) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  if (status != nullptr && atomicExch(&status->timeout_flag, 1) == 0) status->where = site;
+  return false;
+}
+// global -> shared bulk copy (TMA engine, no tensor map): 16-byte aligned both sides,
+// size a multiple of 16; completion is signalled on `bar` by byte count.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- fp16 storage conversion, include/rdna4/fp16.h:37-57 ----------------------
+// Round-to-nearest-even like the hardware conversion, except that NaN becomes a
+// signed infinity (the reference's bit routine has no NaN case).
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float f) {
+  if (f != f) return (uint16_t)(((__float_as_uint(f) >> 16) & 0x8000u) | 0x7c00u);
+  return __half_as_ushort(__float2half_rn(f));
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
+  return __half2float(__ushort_as_half(h));
+}
+
+}  // namespace rd

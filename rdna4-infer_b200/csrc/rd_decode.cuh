@@ -1,0 +1,666 @@
+// Split-KV decode attention for sm_100a: one query token (per grid row) against a
+// quantized KV cache, all 6 query heads of a GQA group sharing every loaded KV tile.
+//
+// Shape of the computation (replaces attn_split_kernel, include/rdna4/attn.cuh:445-560,
+// and the unsplit attn_kernel, :95-185):
+//   * grid (n_splits, n_tok): CTA s owns a contiguous slice of the key tiles and
+//     writes one partial record (m, l, acc[256]) per query head;
+//   * a producer warp streams tiles of TILE keys into a ring of shared-memory stages
+//     with one bulk (TMA-engine) copy per key and tensor -- the n_head_kv rows of a
+//     key are contiguous in the cache -- completion counted on an mbarrier;
+//   * consumer warp (kv head, 16-key group) dequantizes its rows IN REGISTERS straight
+//     into mma.sync m16n8k16 f16 fragments: QK^T with the 16 keys on M and the 6 heads
+//     (padded to 8) on N, then P*V with V^T on M (dims) and the keys on K. The
+//     arithmetic intensity of q4_0 (21 flop/byte) is beyond the FP32 pipe at HBM
+//     speed, hence tensor-core fragments even for a single query token;
+//   * scores live in log2 units (scale*log2e folded into Q), softmax statistics in
+//     f32, online rescale only when a running maximum actually moves.
+//
+// Dequantization in two instructions per pair of values: masking a nibble (or
+// placing a byte) into the low mantissa bits of a half gives the SUBNORMAL n * 2^-24
+// exactly, and one HFMA2 with the block scale turns it into the value:
+//   q4_0: fma(n * 2^-24, d * 2^12, -d * 2^-9)  = d * (n - 8)   * 2^-12
+//   q8_0: fma(u * 2^-24, d * 2^12, -d * 2^-5)  = d * (u - 128) * 2^-12   (u = q ^ 0x80)
+// rounded once, i.e. as exact as an f16 can hold the dequantized value. The common
+// factor 2^-12 keeps every constant a power-of-two multiple of d inside the f16 range
+// (block scales up to 16, i.e. |x| < 128 for q4_0) and is undone for free: Q is
+// pre-multiplied by 2^12 for the scores, the output accumulator is multiplied by
+// 2^12 once at the end.
+//
+// Index freedom used throughout: the contraction index of an MMA can be permuted
+// freely as long as A and B agree, and the M index of P*V (the output dim) can be
+// permuted freely as long as the epilogue writes each value to its true dim. Each
+// loader below therefore defines `dim()` -- which true dim a fragment slot holds --
+// and the Q fragments / epilogue are built from it.
+#pragma once
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace rd {
+
+constexpr uint32_t kH4096 = 0x6C006C00u;    // half2(2^12, 2^12)
+constexpr uint32_t kH256 = 0x5C005C00u;     // half2(2^8, 2^8)
+constexpr uint32_t kHNeg2m9 = 0x98009800u;  // half2(-2^-9, -2^-9)
+constexpr uint32_t kHNeg2m5 = 0xA800A800u;  // half2(-2^-5, -2^-5)
+constexpr float kQuantUnscale = 4096.0f;    // undoes the 2^-12 of the quantized loaders
+
+// Per-block constants of the 4-bit path from the half2 scale d.
+struct Q4Scale {
+  uint32_t lo, hi, c;
+  __device__ __forceinline__ explicit Q4Scale(uint32_t d)
+      : lo(hmul2(d, kH4096)), hi(hmul2(d, kH256)), c(hmul2(d, kHNeg2m9)) {}
+};
+// One word of 8 nibbles, bytes (B0,B1,B2,B3) -> four half2 of d*(n-8)*2^-12:
+//   l0 = (B0.lo, B2.lo), h0 = (B0.hi, B2.hi), l1 = (B1.lo, B3.lo), h1 = (B1.hi, B3.hi)
+__device__ __forceinline__ void dq4(uint32_t x, const Q4Scale &s, uint32_t &l0, uint32_t &h0,
+                                    uint32_t &l1, uint32_t &h1) {
+  const uint32_t y = x >> 8;
+  l0 = hfma2(x & 0x000F000Fu, s.lo, s.c);
+  h0 = hfma2(x & 0x00F000F0u, s.hi, s.c);
+  l1 = hfma2(y & 0x000F000Fu, s.lo, s.c);
+  h1 = hfma2(y & 0x00F000F0u, s.hi, s.c);
+}
+// Per-block constants of the 8-bit path.
+struct Q8Scale {
+  uint32_t m, c;
+  __device__ __forceinline__ explicit Q8Scale(uint32_t d)
+      : m(hmul2(d, kH4096)), c(hmul2(d, kHNeg2m5)) {}
+};
+// Four biased bytes u = q ^ 0x80: lo = (B0, B1), hi = (B2, B3), each d*q*2^-12.
+__device__ __forceinline__ void dq8(uint32_t u, const Q8Scale &s, uint32_t &lo, uint32_t &hi) {
+  lo = hfma2(prmt(u, 0u, 0x4140u), s.m, s.c);
+  hi = hfma2(prmt(u, 0u, 0x4342u), s.m, s.c);
+}
+
+// =============================== K loaders =======================================
+// A fragment of Q*K^T for MMA n (0..15): rows = keys g / g+8 of the 16-key group,
+// k-slots (2t, 2t+1, 2t+8, 2t+9) = four dims chosen by the loader. run() calls
+// mma(n, a0, a1, a2, a3) for n = 0..15. Values come out multiplied by 1/kUnscale.
+template <int T>
+struct KLoad;
+
+template <>
+struct KLoad<RD_KV_Q4_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane t owns blocks 2t and 2t+1 of the row: 36 bytes at 36t (4-byte aligned).
+  __device__ static int dim(int t, int n, int e) {
+    const int x = n >> 1, odd = n & 1;
+    int blk, i0, i2;
+    if (x < 3) {
+      blk = 2 * t; i0 = 4 * x + 2 + odd; i2 = i0 + 2;
+    } else if (x == 3) {
+      blk = 2 * t; i0 = odd; i2 = 14 + odd;
+    } else {
+      blk = 2 * t + 1; i0 = 4 * (x - 4) + odd; i2 = i0 + 2;
+    }
+    return blk * 32 + ((e & 1) ? i2 : i0) + ((e & 2) ? 16 : 0);
+  }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+    uint32_t wg[9], wh[9];
+    row_g += 36 * t;
+    row_h += 36 * t;
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+      wg[i] = lds32(row_g + 4 * i);
+      wh[i] = lds32(row_h + 4 * i);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const uint32_t dg = b == 0 ? prmt(wg[0], wg[0], 0x1010u) : prmt(wg[4], wg[4], 0x3232u);
+      const uint32_t dh = b == 0 ? prmt(wh[0], wh[0], 0x1010u) : prmt(wh[4], wh[4], 0x3232u);
+      const Q4Scale sg(dg), sh(dh);
+#pragma unroll
+      for (int xx = 0; xx < 4; ++xx) {
+        const int x = 4 * b + xx;
+        const uint32_t xg = (x == 3) ? prmt(wg[0], wg[4], 0x5432u) : wg[x + 1];
+        const uint32_t xh = (x == 3) ? prmt(wh[0], wh[4], 0x5432u) : wh[x + 1];
+        uint32_t l0g, h0g, l1g, h1g, l0h, h0h, l1h, h1h;
+        dq4(xg, sg, l0g, h0g, l1g, h1g);
+        dq4(xh, sh, l0h, h0h, l1h, h1h);
+        mma(2 * x, l0g, l0h, h0g, h0h);
+        mma(2 * x + 1, l1g, l1h, h1g, h1h);
+      }
+    }
+  }
+};
+
+template <>
+struct KLoad<RD_KV_Q8_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane t owns blocks 2t and 2t+1: 68 bytes at 68t.
+  __device__ static int dim(int t, int n, int e) {
+    if (n < 7) return (2 * t) * 32 + 4 * n + 2 + e;
+    if (n == 7) return (2 * t) * 32 + (e < 2 ? e : 28 + e);
+    return (2 * t + 1) * 32 + 4 * (n - 8) + e;
+  }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+    uint32_t wg[17], wh[17];
+    row_g += 68 * t;
+    row_h += 68 * t;
+#pragma unroll
+    for (int i = 0; i < 17; ++i) {
+      wg[i] = lds32(row_g + 4 * i);
+      wh[i] = lds32(row_h + 4 * i);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const uint32_t dg = b == 0 ? prmt(wg[0], wg[0], 0x1010u) : prmt(wg[8], wg[8], 0x3232u);
+      const uint32_t dh = b == 0 ? prmt(wh[0], wh[0], 0x1010u) : prmt(wh[8], wh[8], 0x3232u);
+      const Q8Scale sg(dg), sh(dh);
+#pragma unroll
+      for (int xx = 0; xx < 8; ++xx) {
+        const int x = 8 * b + xx;
+        uint32_t xg = (x == 7) ? prmt(wg[0], wg[8], 0x5432u) : wg[x + 1];
+        uint32_t xh = (x == 7) ? prmt(wh[0], wh[8], 0x5432u) : wh[x + 1];
+        xg ^= 0x80808080u;
+        xh ^= 0x80808080u;
+        uint32_t log_, hig, loh, hih;
+        dq8(xg, sg, log_, hig);
+        dq8(xh, sh, loh, hih);
+        mma(x, log_, loh, hig, hih);
+      }
+    }
+  }
+};
+
+template <>
+struct KLoad<RD_KV_F16> {
+  static constexpr float kUnscale = 1.0f;
+  // lane t owns the 16-byte chunks 8*(i>>1) + 2t + (i&1), i = 0..7 (conflict-free with
+  // a key pitch of 16 bytes mod 128).
+  __device__ static int dim(int t, int n, int e) {
+    const int i = n >> 1;
+    const int c = 8 * (i >> 1) + 2 * t + (i & 1);
+    return 8 * c + 4 * (n & 1) + e;
+  }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = 8 * (i >> 1) + 2 * t + (i & 1);
+      const uint4 vg = lds128(row_g + 16 * c);
+      const uint4 vh = lds128(row_h + 16 * c);
+      mma(2 * i, vg.x, vh.x, vg.y, vh.y);
+      mma(2 * i + 1, vg.z, vh.z, vg.w, vh.w);
+    }
+  }
+};
+
+template <>
+struct KLoad<RD_KV_F32> {
+  static constexpr float kUnscale = 1.0f;
+  // lane t owns the 16-byte chunks (4 dims) 4i + t, i = 0..15. Values are rounded to
+  // f16 for the tensor core (f32 caches are a debugging format in the reference).
+  __device__ static int dim(int t, int n, int e) { return 4 * (4 * n + t) + e; }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint4 vg = lds128(row_g + 16 * (4 * i + t));
+      const uint4 vh = lds128(row_h + 16 * (4 * i + t));
+      mma(i, pack_h2(__uint_as_float(vg.x), __uint_as_float(vg.y)),
+          pack_h2(__uint_as_float(vh.x), __uint_as_float(vh.y)),
+          pack_h2(__uint_as_float(vg.z), __uint_as_float(vg.w)),
+          pack_h2(__uint_as_float(vh.z), __uint_as_float(vh.w)));
+    }
+  }
+};
+
+// =============================== V loaders =======================================
+// A fragment of V^T*P for M-tile m (0..15): rows g / g+8 = two true dims chosen by
+// the loader (dim(g, m, r)), k-slots = keys (2t, 2t+1, 2t+8, 2t+9) of the group.
+// rows[j] is the shared address of the stored row of key j of those four. run()
+// calls mma(m, a0, a1, a2, a3) for m = 0..15. Values come out multiplied by 1/kUnscale.
+template <int T>
+struct VLoad;
+
+template <>
+struct VLoad<RD_KV_Q4_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane g owns block g of each key: 18 bytes at 18g, read as 5 aligned words from
+  // (18g & ~3); for odd g the block starts in the upper half of the first word.
+  __device__ static int hidx(int s, int par) { return s <= 6 ? s + 1 - par : (par ? 7 : 0); }
+  __device__ static int dim(int g, int m, int r) {
+    return 32 * g + 2 * hidx(m >> 1, g & 1) + (m & 1) + (r ? 16 : 0);
+  }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+    const uint32_t off = (18u * g) & ~3u;
+    const bool par = g & 1;
+    uint32_t w[4][5];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 5; ++i) w[j][i] = lds32(rows[j] + off + 4 * i);
+    const uint32_t seld = par ? 0x7632u : 0x5410u;
+    const uint32_t dab = prmt(w[0][0], w[1][0], seld);
+    const uint32_t dcd = prmt(w[2][0], w[3][0], seld);
+    const Q4Scale sab(dab), scd(dcd);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      uint32_t xab, xcd;
+      if (s < 7) {
+        const int i = 1 + (s >> 1);
+        const uint32_t sel = (s & 1) ? 0x7632u : 0x5410u;
+        xab = prmt(w[0][i], w[1][i], sel);
+        xcd = prmt(w[2][i], w[3][i], sel);
+      } else {
+        xab = prmt(par ? w[0][4] : w[0][0], par ? w[1][4] : w[1][0], 0x7632u);
+        xcd = prmt(par ? w[2][4] : w[2][0], par ? w[3][4] : w[3][0], 0x7632u);
+      }
+      uint32_t l0a, h0a, l1a, h1a, l0c, h0c, l1c, h1c;
+      dq4(xab, sab, l0a, h0a, l1a, h1a);
+      dq4(xcd, scd, l0c, h0c, l1c, h1c);
+      mma(2 * s, l0a, h0a, l0c, h0c);
+      mma(2 * s + 1, l1a, h1a, l1c, h1c);
+    }
+  }
+};
+
+template <>
+struct VLoad<RD_KV_Q8_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane g owns block g: 34 bytes at 34g, read as 9 aligned words from (34g & ~3).
+  __device__ static int hidx(int s, int par) { return s <= 14 ? s + 1 - par : (par ? 15 : 0); }
+  __device__ static int dim(int g, int m, int r) { return 32 * g + 2 * hidx(m, g & 1) + r; }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+    const uint32_t off = (34u * g) & ~3u;
+    const bool par = g & 1;
+    uint32_t w[4][9];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 9; ++i) w[j][i] = lds32(rows[j] + off + 4 * i);
+    const uint32_t seld = par ? 0x7632u : 0x5410u;
+    const uint32_t dab = prmt(w[0][0], w[1][0], seld);
+    const uint32_t dcd = prmt(w[2][0], w[3][0], seld);
+    const Q8Scale sab(dab), scd(dcd);
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      uint32_t tab, tcd;  // bytes (a.b0, b.b0, a.b1, b.b1) of the 2-byte slot
+      if (s < 15) {
+        const int i = 1 + (s >> 1);
+        const uint32_t sel = (s & 1) ? 0x7362u : 0x5140u;
+        tab = prmt(w[0][i], w[1][i], sel);
+        tcd = prmt(w[2][i], w[3][i], sel);
+      } else {
+        tab = prmt(par ? w[0][8] : w[0][0], par ? w[1][8] : w[1][0], 0x7362u);
+        tcd = prmt(par ? w[2][8] : w[2][0], par ? w[3][8] : w[3][0], 0x7362u);
+      }
+      tab ^= 0x80808080u;
+      tcd ^= 0x80808080u;
+      uint32_t e0a, e1a, e0c, e1c;
+      dq8(tab, sab, e0a, e1a);
+      dq8(tcd, scd, e0c, e1c);
+      mma(s, e0a, e1a, e0c, e1c);
+    }
+  }
+};
+
+template <>
+struct VLoad<RD_KV_F16> {
+  static constexpr float kUnscale = 1.0f;
+  // lane g owns the 16-byte chunks g + 8*ci, ci = 0..3, of each key.
+  __device__ static int dim(int g, int m, int r) { return 8 * (g + 8 * (m >> 2)) + 2 * (m & 3) + r; }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+#pragma unroll
+    for (int ci = 0; ci < 4; ++ci) {
+      const uint32_t o = 16 * (g + 8 * ci);
+      const uint4 a = lds128(rows[0] + o), b = lds128(rows[1] + o);
+      const uint4 c = lds128(rows[2] + o), d = lds128(rows[3] + o);
+      mma(4 * ci + 0, prmt(a.x, b.x, 0x5410u), prmt(a.x, b.x, 0x7632u), prmt(c.x, d.x, 0x5410u),
+          prmt(c.x, d.x, 0x7632u));
+      mma(4 * ci + 1, prmt(a.y, b.y, 0x5410u), prmt(a.y, b.y, 0x7632u), prmt(c.y, d.y, 0x5410u),
+          prmt(c.y, d.y, 0x7632u));
+      mma(4 * ci + 2, prmt(a.z, b.z, 0x5410u), prmt(a.z, b.z, 0x7632u), prmt(c.z, d.z, 0x5410u),
+          prmt(c.z, d.z, 0x7632u));
+      mma(4 * ci + 3, prmt(a.w, b.w, 0x5410u), prmt(a.w, b.w, 0x7632u), prmt(c.w, d.w, 0x5410u),
+          prmt(c.w, d.w, 0x7632u));
+    }
+  }
+};
+
+template <>
+struct VLoad<RD_KV_F32> {
+  static constexpr float kUnscale = 1.0f;
+  // lane g owns the 16-byte chunks (4 dims) g + 8*ci, ci = 0..7.
+  __device__ static int dim(int g, int m, int r) { return 4 * (g + 8 * (m >> 1)) + 2 * (m & 1) + r; }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+#pragma unroll
+    for (int ci = 0; ci < 8; ++ci) {
+      const uint32_t o = 16 * (g + 8 * ci);
+      const uint4 a = lds128(rows[0] + o), b = lds128(rows[1] + o);
+      const uint4 c = lds128(rows[2] + o), d = lds128(rows[3] + o);
+#define RD_F(x) __uint_as_float(x)
+      mma(2 * ci, pack_h2(RD_F(a.x), RD_F(b.x)), pack_h2(RD_F(a.y), RD_F(b.y)),
+          pack_h2(RD_F(c.x), RD_F(d.x)), pack_h2(RD_F(c.y), RD_F(d.y)));
+      mma(2 * ci + 1, pack_h2(RD_F(a.z), RD_F(b.z)), pack_h2(RD_F(a.w), RD_F(b.w)),
+          pack_h2(RD_F(c.z), RD_F(d.z)), pack_h2(RD_F(c.w), RD_F(d.w)));
+#undef RD_F
+    }
+  }
+};
+
+// =============================== kernel ==========================================
+struct DecodeKernelArgs {
+  const float *q;
+  const uint8_t *k;
+  const uint8_t *v;
+  float *partial;
+  const int32_t *pos;
+  int t;
+  int key_begin;
+  int n_head;
+  int nkv;
+  float qscale;  // scale * log2(e)
+  int stages;
+  DeviceStatus *status;
+};
+
+template <int KT, int VT>
+__global__ void __launch_bounds__((4 * key_groups(KT, VT) + 1) * 32, 1)
+decode_kernel(const DecodeKernelArgs p) {
+  constexpr int KG = key_groups(KT, VT);
+  constexpr int TILE = 16 * KG;
+  constexpr int CW = 4 * KG;  // consumer warps; warp CW is the producer
+  constexpr int RK = row_bytes(KT), RV = row_bytes(VT);
+  using KL = KLoad<KT>;
+  using VL = VLoad<VT>;
+  constexpr unsigned FULL = 0xffffffffu;
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int nkv = p.nkv;
+  const int pitch_k = nkv * RK + 16, pitch_v = nkv * RV + 16;
+  const uint32_t stage_bytes = (uint32_t)TILE * (pitch_k + pitch_v);
+  const uint32_t bar_full = smem_u32(smem);                  // kMaxStages x 8 bytes
+  const uint32_t bar_empty = bar_full + 8 * kMaxStages;      // kMaxStages x 8 bytes
+  const uint32_t tiles0 = bar_full + 16 * kMaxStages;        // 128-byte aligned
+
+  const int qt = blockIdx.y;
+  const int t_last = p.pos != nullptr ? p.pos[qt] : p.t;
+  const int n_keys = t_last >= p.key_begin ? t_last - p.key_begin + 1 : 0;
+  const int tiles_total = (n_keys + TILE - 1) / TILE;
+  const int S = gridDim.x, s = blockIdx.x;
+  const int tile_b = (int)(((int64_t)tiles_total * s) / S);
+  const int tile_e = (int)(((int64_t)tiles_total * (s + 1)) / S);
+  const int ntiles = tile_e - tile_b;
+  const int key0 = p.key_begin + tile_b * TILE;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, CW);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  // ---- per-warp state (consumers) ----
+  const int kvh = warp % nkv, gi = warp / nkv;
+  const bool active = warp < CW && gi < KG;
+  float O[16][4];
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+
+  if (warp == CW) {
+    // =========================== producer =======================================
+    const uint32_t kb = (uint32_t)nkv * RK, vb = (uint32_t)nkv * RV;
+    for (int it = 0; it < ntiles; ++it) {
+      const int st = it % p.stages;
+      if (it >= p.stages) {
+        if (!mbar_wait(bar_empty + 8 * st, ((it / p.stages) - 1) & 1, p.status, 1)) {
+          s_abort = 1;
+          break;
+        }
+      }
+      if (*(volatile int *)&s_abort) break;
+      const uint32_t full = bar_full + 8 * st;
+      if (lane == 0) mbar_expect_tx(full, TILE * (kb + vb));
+      __syncwarp();
+      const uint32_t sk = tiles0 + st * stage_bytes;
+      const uint32_t sv = sk + TILE * pitch_k;
+      if (lane < TILE) {
+        int key = key0 + it * TILE + lane;
+        key = key > t_last ? t_last : key;  // tail rows repeat the last key (masked later)
+        bulk_g2s(sk + lane * pitch_k, p.k + (size_t)key * kb, kb, full);
+        bulk_g2s(sv + lane * pitch_v, p.v + (size_t)key * vb, vb, full);
+      }
+    }
+  } else if (active) {
+    // =========================== consumers ======================================
+    // Q fragments (B operand), pre-scaled into log2 units: lane (g, t) holds head g.
+    uint32_t qb[16][2];
+    {
+      const float *qrow = p.q + ((size_t)qt * p.n_head + kvh * kGroup + (g < kGroup ? g : 0)) * kHeadDim;
+      const float qmul = p.qscale * KL::kUnscale;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        float e[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) e[j] = g < kGroup ? qrow[KL::dim(tq, n, j)] * qmul : 0.f;
+        qb[n][0] = pack_h2(e[0], e[1]);
+        qb[n][1] = pack_h2(e[2], e[3]);
+      }
+    }
+
+    for (int it = 0; it < ntiles; ++it) {
+      const int st = it % p.stages;
+      if (!mbar_wait(bar_full + 8 * st, (it / p.stages) & 1, p.status, 2)) {
+        s_abort = 1;
+        break;
+      }
+      const uint32_t sk = tiles0 + st * stage_bytes;
+      const uint32_t sv = sk + TILE * pitch_k;
+      const int kbase = key0 + it * TILE + 16 * gi;  // first key of this warp's group
+
+      // ---- S = K Q^T (16 keys x 8 heads), four accumulator chains ----
+      float Sc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) Sc[i][0] = Sc[i][1] = Sc[i][2] = Sc[i][3] = 0.f;
+      {
+        const uint32_t row_g = sk + (16 * gi + g) * pitch_k + kvh * RK;
+        const uint32_t row_h = row_g + 8 * pitch_k;
+        KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+          mma16816(Sc[n & 3], a0, a1, a2, a3, qb[n][0], qb[n][1]);
+        });
+      }
+      float S0 = (Sc[0][0] + Sc[1][0]) + (Sc[2][0] + Sc[3][0]);
+      float S1 = (Sc[0][1] + Sc[1][1]) + (Sc[2][1] + Sc[3][1]);
+      float S2 = (Sc[0][2] + Sc[1][2]) + (Sc[2][2] + Sc[3][2]);
+      float S3 = (Sc[0][3] + Sc[1][3]) + (Sc[2][3] + Sc[3][3]);
+      if (kbase + 15 > t_last) {  // tail tile: keys beyond the last attended one
+        if (kbase + g > t_last) S0 = S1 = -INFINITY;
+        if (kbase + g + 8 > t_last) S2 = S3 = -INFINITY;
+      }
+
+      // ---- online softmax (per head: columns 2t and 2t+1 of this lane) ----
+      float mx0 = fmaxf(S0, S2), mx1 = fmaxf(S1, S3);
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, o));
+      }
+      if (__any_sync(FULL, mx0 > m0 || mx1 > m1)) {
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = ex2(m0 - (n0 == -INFINITY ? 0.f : n0));
+        const float c1 = ex2(m1 - (n1 == -INFINITY ? 0.f : n1));
+        m0 = n0;
+        m1 = n1;
+        l0 *= c0;
+        l1 *= c1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          O[i][0] *= c0;
+          O[i][1] *= c1;
+          O[i][2] *= c0;
+          O[i][3] *= c1;
+        }
+      }
+      const float ms0 = m0 == -INFINITY ? 0.f : m0, ms1 = m1 == -INFINITY ? 0.f : m1;
+      const float p0 = ex2(S0 - ms0), p1 = ex2(S1 - ms1), p2 = ex2(S2 - ms0), p3 = ex2(S3 - ms1);
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
+      const uint32_t pb0 = movmatrix_trans(pack_h2(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(pack_h2(p2, p3));
+
+      // ---- O^T += V^T P^T (256 dims x 8 heads) ----
+      {
+        uint32_t rows[4];
+        const uint32_t r0 = sv + (16 * gi + 2 * tq) * pitch_v + kvh * RV;
+        rows[0] = r0;
+        rows[1] = r0 + pitch_v;
+        rows[2] = r0 + 8 * pitch_v;
+        rows[3] = r0 + 9 * pitch_v;
+        VL::run(rows, g, [&](int m, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+          mma16816(O[m], a0, a1, a2, a3, pb0, pb1);
+        });
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+    }
+    // row sums: add the 8 key-row lanes of each head column
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l0 += __shfl_xor_sync(FULL, l0, o);
+      l1 += __shfl_xor_sync(FULL, l1, o);
+    }
+    if (VL::kUnscale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        O[i][0] *= VL::kUnscale;
+        O[i][1] *= VL::kUnscale;
+        O[i][2] *= VL::kUnscale;
+        O[i][3] *= VL::kUnscale;
+      }
+    }
+  } else if (warp < CW) {
+    // consumer warp without a (kv head, group) item: only keeps the ring moving
+    for (int it = 0; it < ntiles; ++it) {
+      const int st = it % p.stages;
+      if (!mbar_wait(bar_full + 8 * st, (it / p.stages) & 1, p.status, 3)) {
+        s_abort = 1;
+        break;
+      }
+      if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+    }
+  }
+
+  // ---- combine the key groups of each kv head and write one record per head ----
+  __syncthreads();  // every stage has been consumed (or the CTA is unwinding)
+  if (s_abort) {
+    // Unwinding after a bounded wait ran out: give copies still in flight one more
+    // bounded chance to land before the CTA (and its shared memory) goes away.
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < p.stages && i < ntiles; ++i) {
+        const int last_it = ((ntiles - 1 - i) / p.stages) * p.stages + i;
+        mbar_wait(bar_full + 8 * i, (last_it / p.stages) & 1, nullptr, 0);
+      }
+    }
+    __syncthreads();
+  }
+  float *stg = reinterpret_cast<float *>(smem + 16 * kMaxStages);  // [CW][6][kRec]
+  if (active) {
+    float *mine = stg + (size_t)warp * kGroup * kRec;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int head = 2 * tq + hh;
+      if (head < kGroup) {
+        float *rec = mine + head * kRec;
+        if (g == 0) {
+          rec[0] = hh ? m1 : m0;
+          rec[1] = hh ? l1 : l0;
+        }
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+          rec[2 + VL::dim(g, m, 0)] = O[m][hh];
+          rec[2 + VL::dim(g, m, 1)] = O[m][2 + hh];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int n_items = nkv * kGroup * kHeadDim;
+  for (int idx = threadIdx.x; idx < n_items; idx += blockDim.x) {
+    const int h = idx / kHeadDim, d = idx % kHeadDim;
+    const int hk = h / kGroup, hh = h % kGroup;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < KG; ++w) mm = fmaxf(mm, stg[((w * nkv + hk) * kGroup + hh) * kRec]);
+    float acc = 0.f, ll = 0.f;
+    if (mm != -INFINITY && !s_abort) {
+#pragma unroll
+      for (int w = 0; w < KG; ++w) {
+        const float *rec = stg + ((w * nkv + hk) * kGroup + hh) * kRec;
+        const float wgt = ex2(rec[0] - mm);
+        acc += rec[2 + d] * wgt;
+        ll += rec[1] * wgt;
+      }
+    } else {
+      mm = -INFINITY;
+    }
+    float *out = p.partial + (((size_t)qt * p.n_head + h) * S + s) * kRec;
+    out[2 + d] = acc;
+    if (d == 0) {
+      out[0] = mm == -INFINITY ? -INFINITY : mm * 0.6931471805599453f;  // back to natural log
+      out[1] = ll;
+    }
+  }
+}
+
+// Host side of one (KT, VT) instantiation.
+template <int KT, int VT>
+int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
+  constexpr int KG = key_groups(KT, VT);
+  constexpr int TILE = 16 * KG;
+  const int pitch = key_pitch(KT, a.n_head_kv) + key_pitch(VT, a.n_head_kv);
+  const int stage_bytes = TILE * pitch;
+  int stages = (kSmemBudget - 16 * kMaxStages) / stage_bytes;
+  if (stages < 1) return RD_ERR_UNSUPPORTED;
+  if (stages > kMaxStages) stages = kMaxStages;
+  size_t smem = 16 * kMaxStages + (size_t)stages * stage_bytes;
+  const size_t merge_bytes = 16 * kMaxStages + (size_t)4 * KG * kGroup * kRec * sizeof(float);
+  if (smem < merge_bytes) smem = merge_bytes;
+  static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;
+  if (dev < 8 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(decode_kernel<KT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBudget) != cudaSuccess)
+      return RD_ERR_CUDA;
+    attr_set[dev] = true;
+  } else if (dev >= 8) {
+    if (cudaFuncSetAttribute(decode_kernel<KT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBudget) != cudaSuccess)
+      return RD_ERR_CUDA;
+  }
+  DecodeKernelArgs k;
+  k.q = a.q;
+  k.k = (const uint8_t *)a.k;
+  k.v = (const uint8_t *)a.v;
+  k.partial = a.partial;
+  k.pos = a.pos;
+  k.t = a.t;
+  k.key_begin = a.key_begin;
+  k.n_head = a.n_head;
+  k.nkv = a.n_head_kv;
+  k.qscale = a.scale * 1.4426950408889634f;
+  k.stages = stages;
+  k.status = a.status;
+  const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
+  decode_kernel<KT, VT><<<grid, (4 * KG + 1) * 32, smem, st>>>(k);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+}  // namespace rd

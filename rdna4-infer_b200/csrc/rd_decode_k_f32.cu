@@ -1,0 +1,14 @@
+// Decode-attention kernels whose K cache is f32, one instantiation per V type.
+#include "rd_decode.cuh"
+
+namespace rd {
+int launch_decode_k_f32(int vt, const DecodeArgs &a, cudaStream_t st) {
+  switch (vt) {
+    case RD_KV_F32: return launch_decode_typed<RD_KV_F32, RD_KV_F32>(a, st);
+    case RD_KV_F16: return launch_decode_typed<RD_KV_F32, RD_KV_F16>(a, st);
+    case RD_KV_Q8_0: return launch_decode_typed<RD_KV_F32, RD_KV_Q8_0>(a, st);
+    case RD_KV_Q4_0: return launch_decode_typed<RD_KV_F32, RD_KV_Q4_0>(a, st);
+    default: return RD_ERR_UNSUPPORTED;
+  }
+}
+}  // namespace rd

@@ -1,0 +1,302 @@
+// KV-append (quantize-on-store), synthetic cache fill, RoPE and the gate glue.
+//
+// KV append is the bit-exact part of the path: every block of 32 values must come
+// out byte-identical to the reference quantizers (include/rdna4/kv.h:386-501). The
+// reference runs one THREAD per block with serial 32-element loops; here one WARP
+// owns a block, lane j holds element j, the block statistics are warp shuffles and
+// every lane stores its own byte. The arithmetic is pinned with explicit
+// round-to-nearest intrinsics so that no multiply-add is contracted into an FMA:
+// `x*id + 8.5f` is two roundings in the reference's host mirror, and a fused form
+// changes the byte whenever the sum lands within an ulp of an integer.
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace rd {
+
+// Lane j holds x = element j of the block; writes the block at `dst`.
+template <int T>
+__device__ __forceinline__ void quant_block_warp(float x, uint8_t *dst, int lane) {
+  constexpr unsigned FULL = 0xffffffffu;
+  if (T == RD_KV_Q8_0) {
+    // kv.h:402-411: amax/127, roundf(x*id).
+    float amax = fabsf(x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    if (lane == 0) *(uint16_t *)dst = f32_to_f16_bits(d);
+    dst[2 + lane] = (uint8_t)(int8_t)__float2int_rz(roundf(__fmul_rn(x, id)));
+    return;
+  }
+  if (T == RD_KV_Q4_1) {
+    // kv.h:445-467: affine grid [min, max].
+    float vmin = x, vmax = x;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      vmin = fminf(vmin, __shfl_xor_sync(FULL, vmin, o));
+      vmax = fmaxf(vmax, __shfl_xor_sync(FULL, vmax, o));
+    }
+    const float d = __fdiv_rn(__fsub_rn(vmax, vmin), 15.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int q = __float2int_rz(__fadd_rn(__fmul_rn(__fsub_rn(x, vmin), id), 0.5f));
+    q = q > 15 ? 15 : (q < 0 ? 0 : q);
+    const int qhi = __shfl_down_sync(FULL, q, 16);
+    if (lane == 0) {
+      *(uint16_t *)dst = f32_to_f16_bits(d);
+      *(uint16_t *)(dst + 2) = f32_to_f16_bits(vmin);
+    }
+    if (lane < 16) dst[4 + lane] = (uint8_t)(q | (qhi << 4));
+    return;
+  }
+  // Q4_0 / Q5_0 (kv.h:412-444, 476-499): the SIGNED value of largest magnitude,
+  // first one on ties (the serial scan uses a strict '<'), NaN never selected.
+  float a = (x == x) ? fabsf(x) : -1.0f;
+  float v = x;
+  int idx = lane;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oa = __shfl_xor_sync(FULL, a, o);
+    const float ov = __shfl_xor_sync(FULL, v, o);
+    const int oi = __shfl_xor_sync(FULL, idx, o);
+    if (oa > a || (oa == a && oi < idx)) {
+      a = oa;
+      v = ov;
+      idx = oi;
+    }
+  }
+  const float vmax = a > 0.0f ? v : 0.0f;
+  if (T == RD_KV_Q4_0) {
+    const float d = __fdiv_rn(vmax, -8.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int q = __float2int_rz(__fadd_rn(__fmul_rn(x, id), 8.5f));
+    q = q > 15 ? 15 : (q < 0 ? 0 : q);
+    const int qhi = __shfl_down_sync(FULL, q, 16);
+    if (lane == 0) *(uint16_t *)dst = f32_to_f16_bits(d);
+    if (lane < 16) dst[2 + lane] = (uint8_t)(q | (qhi << 4));
+  } else {  // Q5_0
+    const float d = __fdiv_rn(vmax, -16.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int q = __float2int_rz(__fadd_rn(__fmul_rn(x, id), 16.5f));
+    q = q > 31 ? 31 : (q < 0 ? 0 : q);
+    const int qhi = __shfl_down_sync(FULL, q, 16);
+    const unsigned qh = __ballot_sync(FULL, (q & 0x10) != 0);  // bit j = 5th bit of element j
+    if (lane == 0) *(uint16_t *)dst = f32_to_f16_bits(d);
+    if (lane < 4) dst[2 + lane] = (uint8_t)((qh >> (8 * lane)) & 0xffu);
+    if (lane < 16) dst[6 + lane] = (uint8_t)((q & 0x0f) | ((qhi & 0x0f) << 4));
+  }
+}
+
+template <int T>
+__device__ __forceinline__ void store_block(float x, uint8_t *dst_base, int64_t blk, int lane) {
+  if (T == RD_KV_F32) {
+    ((float *)dst_base)[blk * 32 + lane] = x;
+  } else if (T == RD_KV_F16) {
+    ((uint16_t *)dst_base)[blk * 32 + lane] = f32_to_f16_bits(x);
+  } else {
+    constexpr int BB = row_bytes(T) / 8;
+    quant_block_warp<T>(x, dst_base + blk * BB, lane);
+  }
+}
+
+// RoPE angle factor: freq = base^(-2p/n_rot). The reference calls f32 powf
+// (attn.cuh:39); the correctly rounded value is what a good host libm returns, and
+// a one-ulp difference here moves theta by several milliradians at position 131000,
+// so it is computed in double and rounded once.
+__device__ __forceinline__ float rope_freq(float freq_base, int p, int n_rot) {
+  const float e = -2.0f * (float)p / (float)n_rot;
+  return (float)pow((double)freq_base, (double)e);
+}
+__device__ __forceinline__ void rope_cs(float theta, float &c, float &s) {
+  double sd, cd;
+  sincos((double)theta, &sd, &cd);
+  c = (float)cd;
+  s = (float)sd;
+}
+
+// One warp per 32-element block of K (blockIdx.y == 0) or V (blockIdx.y == 1).
+// With pos != nullptr the K value is rotated first (attn.cuh:30-54): element e of a
+// head pairs with e +- n_rot/2 inside the first n_rot dims, which for n_rot == 64 is
+// the neighbouring block, so the partner is read from global memory.
+template <int KT, int VT>
+__global__ void __launch_bounds__(256)
+kv_append_kernel(const float *__restrict__ ksrc, const float *__restrict__ vsrc,
+                 uint8_t *__restrict__ kdst, uint8_t *__restrict__ vdst, int64_t n_blocks,
+                 int head_dim, int heads_per_tok, const int32_t *__restrict__ pos, int n_rot,
+                 float freq_base) {
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (blk >= n_blocks) return;
+  if (blockIdx.y == 0) {
+    if (ksrc == nullptr) return;
+    const int64_t e = blk * 32 + lane;
+    float x = ksrc[e];
+    if (pos != nullptr) {
+      const int d = (int)(e % head_dim);
+      if (d < n_rot) {
+        const int half = n_rot / 2;
+        const int p = d < half ? d : d - half;
+        const int tok = (int)(e / ((int64_t)head_dim * heads_per_tok));
+        const float theta = (float)pos[tok] * rope_freq(freq_base, p, n_rot);
+        float c, s;
+        rope_cs(theta, c, s);
+        const float other = ksrc[d < half ? e + half : e - half];
+        // (x0, x1) -> (x0*c - x1*s, x0*s + x1*c), products rounded separately
+        x = d < half ? __fsub_rn(__fmul_rn(x, c), __fmul_rn(other, s))
+                     : __fadd_rn(__fmul_rn(other, s), __fmul_rn(x, c));
+      }
+    }
+    store_block<KT>(x, kdst, blk, lane);
+  } else {
+    if (vsrc == nullptr) return;
+    store_block<VT>(vsrc[blk * 32 + lane], vdst, blk, lane);
+  }
+}
+
+// include/rdna4/kv.h:508-513.
+__device__ __forceinline__ float kv_rand_dev(unsigned idx, unsigned seed) {
+  unsigned h = idx * 2654435761u ^ seed * 2246822519u;
+  h ^= h >> 13;
+  h *= 1274126177u;
+  return __fsub_rn(__fdiv_rn((float)(h >> 8), 8388608.0f), 1.0f);
+}
+
+template <int T>
+__global__ void __launch_bounds__(256)
+kv_fill_kernel(uint8_t *__restrict__ cache, int64_t n_blocks, unsigned seed) {
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (blk >= n_blocks) return;
+  // rows are contiguous and head_dim is a multiple of 32, so block b of the cache
+  // holds elements 32b..32b+31 of the flat index the hash is fed with.
+  const float x = kv_rand_dev((unsigned)(blk * 32 + lane), seed);
+  store_block<T>(x, cache, blk, lane);
+}
+
+__global__ void rope_kernel(float *__restrict__ x, int n_tok, int n_heads, int head_dim, int n_rot,
+                            float freq_base, const int32_t *__restrict__ pos) {
+  const int pairs = n_rot / 2;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)n_tok * n_heads * pairs) return;
+  const int p = (int)(idx % pairs);
+  const int64_t th = idx / pairs;  // token * n_heads + head
+  const int tok = (int)(th / n_heads);
+  const float theta = (float)pos[tok] * rope_freq(freq_base, p, n_rot);
+  float c, s;
+  rope_cs(theta, c, s);
+  float *base = x + th * head_dim;
+  const float x0 = base[p], x1 = base[p + pairs];
+  base[p] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+  base[p + pairs] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
+__global__ void deinterleave_kernel(const float4 *__restrict__ yq, float4 *__restrict__ q,
+                                    float4 *__restrict__ gate, int64_t n_rows, int hd4) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows * hd4) return;
+  const int64_t r = i / hd4;
+  const int d = (int)(i % hd4);
+  q[i] = yq[r * 2 * hd4 + d];
+  gate[i] = yq[r * 2 * hd4 + hd4 + d];
+}
+
+__global__ void sigmoid_gate_kernel(float *__restrict__ g, float *__restrict__ y, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float s = __fdiv_rn(1.0f, 1.0f + expf(-g[i]));
+  g[i] = s;
+  y[i] = y[i] * s;
+}
+
+// ---- host launchers ---------------------------------------------------------------
+
+template <int KT>
+static int append_dispatch_v(int vt, const float *ks, const float *vs, uint8_t *kd, uint8_t *vd,
+                             int64_t n_blocks, int head_dim, int heads_per_tok, const int32_t *pos,
+                             int n_rot, float freq_base, cudaStream_t st) {
+  const dim3 grid((unsigned)((n_blocks * 32 + 255) / 256), 2);
+#define RD_V(VT)                                                                              \
+  case VT:                                                                                    \
+    kv_append_kernel<KT, VT><<<grid, 256, 0, st>>>(ks, vs, kd, vd, n_blocks, head_dim,        \
+                                                   heads_per_tok, pos, n_rot, freq_base);     \
+    break;
+  switch (vt) {
+    RD_V(RD_KV_F32)
+    RD_V(RD_KV_F16)
+    RD_V(RD_KV_Q8_0)
+    RD_V(RD_KV_Q4_0)
+    RD_V(RD_KV_Q5_0)
+    RD_V(RD_KV_Q4_1)
+    default: return RD_ERR_TYPE;
+  }
+#undef RD_V
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_kv_append(int kt, int vt, const float *ks, const float *vs, void *kd, void *vd,
+                     int64_t width, int head_dim, int heads_per_tok, const int32_t *pos, int n_rot,
+                     float freq_base, cudaStream_t st) {
+  const int64_t n_blocks = width / 32;
+  if (n_blocks == 0) return RD_OK;
+#define RD_K(KT)                                                                               \
+  case KT:                                                                                     \
+    return append_dispatch_v<KT>(vt, ks, vs, (uint8_t *)kd, (uint8_t *)vd, n_blocks, head_dim, \
+                                 heads_per_tok, pos, n_rot, freq_base, st);
+  switch (kt) {
+    RD_K(RD_KV_F32)
+    RD_K(RD_KV_F16)
+    RD_K(RD_KV_Q8_0)
+    RD_K(RD_KV_Q4_0)
+    RD_K(RD_KV_Q5_0)
+    RD_K(RD_KV_Q4_1)
+    default: return RD_ERR_TYPE;
+  }
+#undef RD_K
+}
+
+int launch_kv_fill(int type, void *cache, int64_t n_rows, int head_dim, uint32_t seed,
+                   cudaStream_t st) {
+  const int64_t n_blocks = n_rows * (head_dim / 32);
+  if (n_blocks == 0) return RD_OK;
+  const unsigned grid = (unsigned)((n_blocks * 32 + 255) / 256);
+#define RD_F(T)                                                                       \
+  case T:                                                                             \
+    kv_fill_kernel<T><<<grid, 256, 0, st>>>((uint8_t *)cache, n_blocks, seed);        \
+    break;
+  switch (type) {
+    RD_F(RD_KV_F32)
+    RD_F(RD_KV_F16)
+    RD_F(RD_KV_Q8_0)
+    RD_F(RD_KV_Q4_0)
+    RD_F(RD_KV_Q5_0)
+    RD_F(RD_KV_Q4_1)
+    default: return RD_ERR_TYPE;
+  }
+#undef RD_F
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float freq_base,
+                const int32_t *pos, cudaStream_t st) {
+  const int64_t total = (int64_t)n_tok * n_heads * (n_rot / 2);
+  if (total == 0) return RD_OK;
+  rope_kernel<<<(unsigned)((total + 127) / 128), 128, 0, st>>>(x, n_tok, n_heads, head_dim, n_rot,
+                                                               freq_base, pos);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_deinterleave(const float *yq, float *q, float *gate, int64_t n_rows, int head_dim,
+                        cudaStream_t st) {
+  const int64_t n = n_rows * (head_dim / 4);
+  if (n == 0) return RD_OK;
+  deinterleave_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      (const float4 *)yq, (float4 *)q, (float4 *)gate, n_rows, head_dim / 4);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_sigmoid_gate(float *g, float *y, int64_t n, cudaStream_t st) {
+  if (n == 0) return RD_OK;
+  sigmoid_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, y, n);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+}  // namespace rd

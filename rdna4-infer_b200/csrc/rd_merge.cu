@@ -1,0 +1,113 @@
+// Log-sum-exp merge of split-KV partial records (replaces attn_merge_kernel and
+// attn_merge_batch_kernel, include/rdna4/attn.cuh:563-590,795-827).
+//
+//   mm = max_s m_s;  out = sum_s acc_s * e^(m_s - mm) / sum_s l_s * e^(m_s - mm)
+//
+// A row whose records are all empty (m = -inf) gives zeros, never NaN. The reference
+// runs one 32-lane warp per head over at most 16 records; here a head can have one
+// record per SM, so a CTA owns (row, 64-dim quarter) and spreads the records over 16
+// thread groups: 4 * n_rows CTAs of 1024 threads keep the read of the partial buffer
+// wide enough to stay off the critical path of a ~25 us decode step.
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace rd {
+
+constexpr int kMergeDims = 64;    // dims per CTA
+constexpr int kMergeGroups = 16;  // record groups per CTA
+
+// MODE 0: normalised output (optionally gated). MODE 1: un-normalised record out.
+template <int MODE>
+__global__ void __launch_bounds__(kMergeDims *kMergeGroups)
+merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_in, int n_out,
+             float *__restrict__ gate) {
+  __shared__ float s_l[kMergeGroups];
+  __shared__ float s_acc[kMergeGroups][kMergeDims];
+  __shared__ float s_mm;
+
+  const int row = blockIdx.x;
+  const int quarter = blockIdx.y;
+  const int j = MODE == 1 ? blockIdx.z : 0;  // output record index
+  const int tx = threadIdx.x % kMergeDims, ty = threadIdx.x / kMergeDims;
+  const int lo = MODE == 1 ? (int)(((int64_t)n_in * j) / n_out) : 0;
+  const int hi = MODE == 1 ? (int)(((int64_t)n_in * (j + 1)) / n_out) : n_in;
+  const float *base = partial + (size_t)row * n_in * kRec;
+
+  // pass 1: the maximum over this output's records
+  float mx = -INFINITY;
+  for (int s = lo + threadIdx.x; s < hi; s += blockDim.x) mx = fmaxf(mx, base[(size_t)s * kRec]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) s_acc[0][threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = -INFINITY;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, s_acc[0][i]);
+    s_mm = m;
+  }
+  __syncthreads();
+  const float mm = s_mm;
+  __syncthreads();
+
+  // pass 2: group ty walks records lo+ty, lo+ty+16, ...
+  float acc = 0.f, ll = 0.f;
+  if (mm != -INFINITY) {
+    for (int s = lo + ty; s < hi; s += kMergeGroups) {
+      const float *rec = base + (size_t)s * kRec;
+      const float w = expf(rec[0] - mm);  // an empty record (m = -inf) weighs 0
+      if (w > 0.f) {                      // ... and is never read, whatever it holds
+        acc = fmaf(rec[2 + quarter * kMergeDims + tx], w, acc);
+        if (tx == 0) ll = fmaf(rec[1], w, ll);
+      }
+    }
+  }
+  s_acc[ty][tx] = acc;
+  if (tx == 0) s_l[ty] = ll;
+  __syncthreads();
+  if (ty == 0) {
+    float a = 0.f, l = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMergeGroups; ++i) {
+      a += s_acc[i][tx];
+      l += s_l[i];
+    }
+    const int d = quarter * kMergeDims + tx;
+    if (MODE == 0) {
+      float o = (mm != -INFINITY && l > 0.f) ? a / l : 0.f;
+      float *op = out + (size_t)row * kHeadDim + d;
+      if (gate != nullptr) {
+        float *gp = gate + (size_t)row * kHeadDim + d;
+        const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
+        *gp = sg;
+        o *= sg;
+      }
+      *op = o;
+    } else {
+      float *rec = out + ((size_t)row * n_out + j) * kRec;
+      rec[2 + d] = a;
+      if (d == 0) {
+        rec[0] = mm;
+        rec[1] = l;
+      }
+    }
+  }
+}
+
+int launch_merge(const float *partial, float *out, int n_rows, int n_splits, float *gate,
+                 cudaStream_t st) {
+  if (n_rows == 0) return RD_OK;
+  const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, 1);
+  merge_kernel<0><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, out, n_splits, 1, gate);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_merge_records(const float *partial, float *records, int n_rows, int n_in, int n_out,
+                         cudaStream_t st) {
+  if (n_rows == 0) return RD_OK;
+  const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, (unsigned)n_out);
+  merge_kernel<1><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, records, n_in, n_out,
+                                                               nullptr);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+}  // namespace rd
