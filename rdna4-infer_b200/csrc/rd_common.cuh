@@ -1,5 +1,6 @@
 // Shared device/host helpers of the sm_100a attention / KV-cache library.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -155,6 +156,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
           "r"(dst_smem),
       "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// global -> shared 2-D tile copy through a tensor map: box rows land densely in shared
+// memory (128-byte aligned), rows outside the tensor are filled with zeros. x is in
+// elements of the map's data type and must keep x * element size a multiple of 16.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];" ::"r"(dst_smem),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {

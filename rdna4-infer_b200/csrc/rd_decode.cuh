@@ -34,6 +34,8 @@
 // and the Q fragments / epilogue are built from it.
 #pragma once
 #include "rd_common.cuh"
+#include <string.h>
+
 #include "rd_internal.h"
 
 namespace rd {
@@ -348,6 +350,12 @@ struct VLoad<RD_KV_F32> {
 
 // =============================== kernel ==========================================
 struct DecodeKernelArgs {
+  // Tensor maps over the K / V caches viewed as [n_keys][n_head_kv * row_bytes / 4]
+  // u32 with a box of [TILE keys][one kv head's row]; used when k_tmap / v_tmap is set.
+  alignas(64) CUtensorMap tm_k;
+  alignas(64) CUtensorMap tm_v;
+  int k_tmap;
+  int v_tmap;
   const float *q;
   const uint8_t *k;
   const uint8_t *v;
@@ -364,7 +372,7 @@ struct DecodeKernelArgs {
 
 template <int KT, int VT>
 __global__ void __launch_bounds__((4 * key_groups(KT, VT) + 1) * 32, 1)
-decode_kernel(const DecodeKernelArgs p) {
+decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   constexpr int KG = key_groups(KT, VT);
   constexpr int TILE = 16 * KG;
   constexpr int CW = 4 * KG;  // consumer warps; warp CW is the producer
@@ -381,6 +389,11 @@ decode_kernel(const DecodeKernelArgs p) {
   const int nkv = p.nkv;
   const int pitch_k = nkv * RK + 16, pitch_v = nkv * RV + 16;
   const uint32_t stage_bytes = (uint32_t)TILE * (pitch_k + pitch_v);
+  // Shared-memory tile layout per tensor. Bulk copies (one per key): [key][kv head rows
+  // + 16 bytes]. Tensor-map tiles (one per kv head): [kv head][key][row], dense.
+  const uint32_t k_key_stride = p.k_tmap ? RK : pitch_k, k_head_stride = p.k_tmap ? TILE * RK : RK;
+  const uint32_t v_key_stride = p.v_tmap ? RV : pitch_v, v_head_stride = p.v_tmap ? TILE * RV : RV;
+  const uint32_t v_tile_off = p.k_tmap ? TILE * nkv * RK : TILE * pitch_k;
   const uint32_t bar_full = smem_u32(smem);                  // kMaxStages x 8 bytes
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;      // kMaxStages x 8 bytes
   const uint32_t tiles0 = bar_full + 16 * kMaxStages;        // 128-byte aligned
@@ -429,11 +442,18 @@ decode_kernel(const DecodeKernelArgs p) {
       if (lane == 0) mbar_expect_tx(full, TILE * (kb + vb));
       __syncwarp();
       const uint32_t sk = tiles0 + st * stage_bytes;
-      const uint32_t sv = sk + TILE * pitch_k;
-      if (lane < TILE) {
-        int key = key0 + it * TILE + lane;
-        key = key > t_last ? t_last : key;  // tail rows repeat the last key (masked later)
+      const uint32_t sv = sk + v_tile_off;
+      const int row0 = key0 + it * TILE;
+      if (p.k_tmap) {
+        if (lane < nkv) tma_load_2d(sk + lane * k_head_stride, &p.tm_k, lane * (RK / 4), row0, full);
+      } else if (lane < TILE) {
+        const int key = row0 + lane > t_last ? t_last : row0 + lane;  // tail rows repeat the last key
         bulk_g2s(sk + lane * pitch_k, p.k + (size_t)key * kb, kb, full);
+      }
+      if (p.v_tmap) {
+        if (lane < nkv) tma_load_2d(sv + lane * v_head_stride, &p.tm_v, lane * (RV / 4), row0, full);
+      } else if (lane < TILE) {
+        const int key = row0 + lane > t_last ? t_last : row0 + lane;
         bulk_g2s(sv + lane * pitch_v, p.v + (size_t)key * vb, vb, full);
       }
     }
@@ -461,7 +481,7 @@ decode_kernel(const DecodeKernelArgs p) {
         break;
       }
       const uint32_t sk = tiles0 + st * stage_bytes;
-      const uint32_t sv = sk + TILE * pitch_k;
+      const uint32_t sv = sk + v_tile_off;
       const int kbase = key0 + it * TILE + 16 * gi;  // first key of this warp's group
 
       // ---- S = K Q^T (16 keys x 8 heads), four accumulator chains ----
@@ -469,8 +489,8 @@ decode_kernel(const DecodeKernelArgs p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) Sc[i][0] = Sc[i][1] = Sc[i][2] = Sc[i][3] = 0.f;
       {
-        const uint32_t row_g = sk + (16 * gi + g) * pitch_k + kvh * RK;
-        const uint32_t row_h = row_g + 8 * pitch_k;
+        const uint32_t row_g = sk + (16 * gi + g) * k_key_stride + kvh * k_head_stride;
+        const uint32_t row_h = row_g + 8 * k_key_stride;
         KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
           mma16816(Sc[n & 3], a0, a1, a2, a3, qb[n][0], qb[n][1]);
         });
@@ -518,11 +538,11 @@ decode_kernel(const DecodeKernelArgs p) {
       // ---- O^T += V^T P^T (256 dims x 8 heads) ----
       {
         uint32_t rows[4];
-        const uint32_t r0 = sv + (16 * gi + 2 * tq) * pitch_v + kvh * RV;
+        const uint32_t r0 = sv + (16 * gi + 2 * tq) * v_key_stride + kvh * v_head_stride;
         rows[0] = r0;
-        rows[1] = r0 + pitch_v;
-        rows[2] = r0 + 8 * pitch_v;
-        rows[3] = r0 + 9 * pitch_v;
+        rows[1] = r0 + v_key_stride;
+        rows[2] = r0 + 8 * v_key_stride;
+        rows[3] = r0 + 9 * v_key_stride;
         VL::run(rows, g, [&](int m, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
           mma16816(O[m], a0, a1, a2, a3, pb0, pb1);
         });
@@ -646,6 +666,17 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
       return RD_ERR_CUDA;
   }
   DecodeKernelArgs k;
+  memset(&k, 0, sizeof(k));
+  // Quantized rows are small (144 / 272 bytes per kv head), so their tiles come in as
+  // one tensor-map copy per kv head; f16 / f32 rows are large enough for one plain bulk
+  // copy per key into the padded layout their loaders want. Tensor maps need the key
+  // count on the host, so launches that take it from a device array use bulk copies.
+  const bool host_keys = a.pos == nullptr;
+  const int64_t n_rows = (int64_t)a.t + 1;
+  k.k_tmap = host_keys && n_rows > 0 && KT >= RD_KV_Q8_0 &&
+             encode_kv_tmap(&k.tm_k, a.k, KT, a.n_head_kv, n_rows, TILE) == RD_OK;
+  k.v_tmap = host_keys && n_rows > 0 && VT >= RD_KV_Q8_0 &&
+             encode_kv_tmap(&k.tm_v, a.v, VT, a.n_head_kv, n_rows, TILE) == RD_OK;
   k.q = a.q;
   k.k = (const uint8_t *)a.k;
   k.v = (const uint8_t *)a.v;

@@ -43,6 +43,13 @@ int launch_decode(int kt, int vt, const DecodeArgs &a, cudaStream_t st);
 // Keys per tile of the (kt, vt) kernel: the granularity of the key split.
 int decode_tile_keys(int kt, int vt);
 
+// ---- rd_tmap.cu
+// Tensor map over a KV cache viewed as u32 [n_rows][n_head_kv * row_bytes / 4] with a
+// box of [tile_rows][row_bytes / 4] (one kv head), no swizzle, zero fill outside.
+// Returns RD_OK, or an error if the driver entry point is unavailable or refuses.
+int encode_kv_tmap(void *tmap_out, const void *base, int type, int n_head_kv, int64_t n_rows,
+                   int tile_rows);
+
 // ---- rd_merge.cu
 // partial [n_rows][n_splits][258] -> out [n_rows][256]; optional fused sigmoid gate.
 int launch_merge(const float *partial, float *out, int n_rows, int n_splits, float *gate,

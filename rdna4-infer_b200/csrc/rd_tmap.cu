@@ -1,0 +1,46 @@
+// Host-side construction of TMA tensor maps for KV-cache tiles. The driver's encoder
+// is reached through cudaGetDriverEntryPoint, so the library links against the CUDA
+// runtime only.
+#include <mutex>
+
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace rd {
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_once;
+
+void resolve() {
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    g_encode = (EncodeTiledFn)fn;
+}
+}  // namespace
+
+int encode_kv_tmap(void *tmap_out, const void *base, int type, int n_head_kv, int64_t n_rows,
+                   int tile_rows) {
+  std::call_once(g_once, resolve);
+  if (g_encode == nullptr) return RD_ERR_CUDA;
+  const int rb = row_bytes(type);
+  if (rb == 0 || rb % 16 != 0 || rb / 4 > 256 || tile_rows > 256 || n_rows < 1) return RD_ERR_SHAPE;
+  if (((uintptr_t)base & 15) != 0) return RD_ERR_ALIGN;
+  const cuuint64_t dims[2] = {(cuuint64_t)n_head_kv * (rb / 4), (cuuint64_t)n_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)n_head_kv * rb};  // bytes between keys
+  const cuuint32_t box[2] = {(cuuint32_t)(rb / 4), (cuuint32_t)tile_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode((CUtensorMap *)tmap_out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2,
+                              const_cast<void *>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RD_OK : RD_ERR_CUDA;
+}
+
+}  // namespace rd
