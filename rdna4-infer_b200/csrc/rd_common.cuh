@@ -41,10 +41,23 @@ constexpr int kSmemBudget = 220 * 1024;  // per CTA, of the 227 KB an sm_100 CTA
 // n_head_kv == 4 (pitch = 16 or 80 bytes mod 128).
 __host__ __device__ constexpr int key_pitch(int type, int nkv) { return nkv * row_bytes(type) + 16; }
 
-// 16-key groups per tile: 2 when three 32-key stages fit the budget, else 1.
+// Shared memory in front of the tile ring: 16 mbarriers, then the query rows of the
+// CTA's token pre-scaled in f32, [head][260] with dim d at d + (d >> 6) (the skew keeps
+// the fragment build free of bank conflicts).
+constexpr int kQRowFloats = 260;
+constexpr int kQStageBytes = 4 * kGroup * kQRowFloats * 4;       // n_head_kv <= 4
+constexpr int kRingOffset = 16 * kMaxStages + kQStageBytes;      // multiple of 128
+
+// 16-key groups per tile = consumer warps per kv head: as many (up to 3) as leave room
+// for three stages -- more resident warps hide the dequantize -> MMA latency better.
 __host__ __device__ constexpr int key_groups(int kt, int vt) {
-  return 3 * 32 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget ? 2 : 1;
+  return 3 * 48 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget - kRingOffset   ? 3
+         : 3 * 32 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget - kRingOffset ? 2
+                                                                                       : 1;
 }
+// Floats of one warp's slot in the epilogue staging: 6 heads x (m, l, 8 blocks x 33).
+constexpr int kStgHead = 2 + 8 * 33;
+constexpr int kStgWarp = kGroup * kStgHead;
 
 // ---- PTX helpers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

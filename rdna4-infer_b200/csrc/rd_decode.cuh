@@ -34,7 +34,10 @@
 // and the Q fragments / epilogue are built from it.
 #pragma once
 #include "rd_common.cuh"
+#include <stdlib.h>
 #include <string.h>
+
+#include <type_traits>
 
 #include "rd_internal.h"
 
@@ -350,8 +353,8 @@ struct VLoad<RD_KV_F32> {
 
 // =============================== kernel ==========================================
 struct DecodeKernelArgs {
-  // Tensor maps over the K / V caches viewed as [n_keys][n_head_kv * row_bytes / 4]
-  // u32 with a box of [TILE keys][one kv head's row]; used when k_tmap / v_tmap is set.
+  // Tensor maps over the K / V caches (see encode_kv_tmap): one box = one tile of TILE
+  // keys in the padded shared-memory layout; used when k_tmap / v_tmap is set.
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
   int k_tmap;
@@ -367,6 +370,8 @@ struct DecodeKernelArgs {
   int nkv;
   float qscale;  // scale * log2(e)
   int stages;
+  int debug;  // 0 normal; timing experiments only, bit mask: 1 consumers skip all math, 2 producer
+              // skips the copies, 4 skip QK, 8 skip PV, 16 skip the softmax
   DeviceStatus *status;
 };
 
@@ -389,14 +394,15 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const int nkv = p.nkv;
   const int pitch_k = nkv * RK + 16, pitch_v = nkv * RV + 16;
   const uint32_t stage_bytes = (uint32_t)TILE * (pitch_k + pitch_v);
-  // Shared-memory tile layout per tensor. Bulk copies (one per key): [key][kv head rows
-  // + 16 bytes]. Tensor-map tiles (one per kv head): [kv head][key][row], dense.
-  const uint32_t k_key_stride = p.k_tmap ? RK : pitch_k, k_head_stride = p.k_tmap ? TILE * RK : RK;
-  const uint32_t v_key_stride = p.v_tmap ? RV : pitch_v, v_head_stride = p.v_tmap ? TILE * RV : RV;
-  const uint32_t v_tile_off = p.k_tmap ? TILE * nkv * RK : TILE * pitch_k;
+  // Shared-memory tile layout of both tensors: [key][the kv heads' rows + 16 bytes],
+  // written either by one tensor-map copy per tile or by one bulk copy per key.
+  const uint32_t k_key_stride = pitch_k, k_head_stride = RK;
+  const uint32_t v_key_stride = pitch_v, v_head_stride = RV;
+  const uint32_t v_tile_off = TILE * pitch_k;
   const uint32_t bar_full = smem_u32(smem);                  // kMaxStages x 8 bytes
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;      // kMaxStages x 8 bytes
-  const uint32_t tiles0 = bar_full + 16 * kMaxStages;        // 128-byte aligned
+  float *qstage = reinterpret_cast<float *>(smem + 16 * kMaxStages);
+  const uint32_t tiles0 = bar_full + kRingOffset;            // 128-byte aligned
 
   const int qt = blockIdx.y;
   const int t_last = p.pos != nullptr ? p.pos[qt] : p.t;
@@ -417,41 +423,71 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     fence_barrier_init();
   }
   __syncthreads();
+  if (warp < CW) {
+    // Query rows of this token -> shared memory, pre-scaled into log2 units (and by the
+    // loader's fixed-point factor), coalesced; the producer warp is already streaming.
+    const float qmul = p.qscale * KL::kUnscale;
+    const float4 *q4 = reinterpret_cast<const float4 *>(p.q + (size_t)qt * p.n_head * kHeadDim);
+    for (int i = threadIdx.x; i < nkv * kGroup * (kHeadDim / 4); i += CW * 32) {
+      const int head = i >> 6, c4 = i & 63;
+      const float4 v = q4[i];
+      float *dst = qstage + head * kQRowFloats + 4 * c4 + (c4 >> 4);
+      dst[0] = v.x * qmul;
+      dst[1] = v.y * qmul;
+      dst[2] = v.z * qmul;
+      dst[3] = v.w * qmul;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+  }
 
   // ---- per-warp state (consumers) ----
   const int kvh = warp % nkv, gi = warp / nkv;
   const bool active = warp < CW && gi < KG;
   float O[16][4];
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  // Running maxima start at a large finite negative instead of -inf: exp2(m_old - m_new)
+  // and exp2(s - m) then need no special cases (an all-masked step keeps p = 0).
+  constexpr float kNegBig = -1.0e30f;
+  float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
 
   if (warp == CW) {
     // =========================== producer =======================================
     const uint32_t kb = (uint32_t)nkv * RK, vb = (uint32_t)nkv * RV;
-    for (int it = 0; it < ntiles; ++it) {
-      const int st = it % p.stages;
+    int st = 0;
+    uint32_t ph = 1;  // parity of the previous use of the stage (no wait on the first lap)
+    for (int it = 0; it < ntiles; ++it, ++st) {
+      if (st == p.stages) {
+        st = 0;
+        ph ^= 1;
+      }
       if (it >= p.stages) {
-        if (!mbar_wait(bar_empty + 8 * st, ((it / p.stages) - 1) & 1, p.status, 1)) {
+        if (!mbar_wait(bar_empty + 8 * st, ph, p.status, 1)) {
           s_abort = 1;
           break;
         }
       }
       if (*(volatile int *)&s_abort) break;
       const uint32_t full = bar_full + 8 * st;
-      if (lane == 0) mbar_expect_tx(full, TILE * (kb + vb));
+      // a tensor-map box counts its zero-filled padding columns too
+      if (p.debug & 2) {
+        if (lane == 0) mbar_arrive(full);
+        continue;
+      }
+      if (lane == 0)
+        mbar_expect_tx(full, TILE * ((p.k_tmap ? pitch_k : kb) + (p.v_tmap ? pitch_v : vb)));
       __syncwarp();
       const uint32_t sk = tiles0 + st * stage_bytes;
       const uint32_t sv = sk + v_tile_off;
       const int row0 = key0 + it * TILE;
       if (p.k_tmap) {
-        if (lane < nkv) tma_load_2d(sk + lane * k_head_stride, &p.tm_k, lane * (RK / 4), row0, full);
+        if (lane == 0) tma_load_2d(sk, &p.tm_k, 0, row0, full);
       } else if (lane < TILE) {
         const int key = row0 + lane > t_last ? t_last : row0 + lane;  // tail rows repeat the last key
         bulk_g2s(sk + lane * pitch_k, p.k + (size_t)key * kb, kb, full);
       }
       if (p.v_tmap) {
-        if (lane < nkv) tma_load_2d(sv + lane * v_head_stride, &p.tm_v, lane * (RV / 4), row0, full);
+        if (lane == 0) tma_load_2d(sv, &p.tm_v, 0, row0, full);
       } else if (lane < TILE) {
         const int key = row0 + lane > t_last ? t_last : row0 + lane;
         bulk_g2s(sv + lane * pitch_v, p.v + (size_t)key * vb, vb, full);
@@ -462,50 +498,81 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     // Q fragments (B operand), pre-scaled into log2 units: lane (g, t) holds head g.
     uint32_t qb[16][2];
     {
-      const float *qrow = p.q + ((size_t)qt * p.n_head + kvh * kGroup + (g < kGroup ? g : 0)) * kHeadDim;
-      const float qmul = p.qscale * KL::kUnscale;
+      const float *qrow = qstage + (kvh * kGroup + (g < kGroup ? g : 0)) * kQRowFloats;
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
         float e[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) e[j] = g < kGroup ? qrow[KL::dim(tq, n, j)] * qmul : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          const int dd = KL::dim(tq, n, j);
+          e[j] = g < kGroup ? qrow[dd + (dd >> 6)] : 0.f;
+        }
         qb[n][0] = pack_h2(e[0], e[1]);
         qb[n][1] = pack_h2(e[2], e[3]);
       }
     }
 
-    for (int it = 0; it < ntiles; ++it) {
-      const int st = it % p.stages;
-      if (!mbar_wait(bar_full + 8 * st, (it / p.stages) & 1, p.status, 2)) {
-        s_abort = 1;
-        break;
-      }
-      const uint32_t sk = tiles0 + st * stage_bytes;
-      const uint32_t sv = sk + v_tile_off;
-      const int kbase = key0 + it * TILE + 16 * gi;  // first key of this warp's group
-
-      // ---- S = K Q^T (16 keys x 8 heads), four accumulator chains ----
-      float Sc[4][4];
+    // One step consumes the warp's 16-key group of NG consecutive tiles. Two groups per
+    // step give the scheduler two independent dequantize->MMA streams per warp (there
+    // are only two consumer warps per scheduler) and halve the softmax bookkeeping.
+    int cst = 0;        // ring stage of the next tile to consume
+    uint32_t cph = 0;   // and the parity its full barrier completes with
+    auto step = [&](auto ngc, const int it0) -> bool {
+      constexpr int NG = decltype(ngc)::value;
+      uint32_t sk[NG], sv[NG], bar_e[NG];
+      int kbase[NG];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) Sc[i][0] = Sc[i][1] = Sc[i][2] = Sc[i][3] = 0.f;
-      {
-        const uint32_t row_g = sk + (16 * gi + g) * k_key_stride + kvh * k_head_stride;
-        const uint32_t row_h = row_g + 8 * k_key_stride;
-        KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-          mma16816(Sc[n & 3], a0, a1, a2, a3, qb[n][0], qb[n][1]);
-        });
-      }
-      float S0 = (Sc[0][0] + Sc[1][0]) + (Sc[2][0] + Sc[3][0]);
-      float S1 = (Sc[0][1] + Sc[1][1]) + (Sc[2][1] + Sc[3][1]);
-      float S2 = (Sc[0][2] + Sc[1][2]) + (Sc[2][2] + Sc[3][2]);
-      float S3 = (Sc[0][3] + Sc[1][3]) + (Sc[2][3] + Sc[3][3]);
-      if (kbase + 15 > t_last) {  // tail tile: keys beyond the last attended one
-        if (kbase + g > t_last) S0 = S1 = -INFINITY;
-        if (kbase + g + 8 > t_last) S2 = S3 = -INFINITY;
+      for (int j = 0; j < NG; ++j) {
+        if (!mbar_wait(bar_full + 8 * cst, cph, p.status, 2)) return false;
+        sk[j] = tiles0 + cst * stage_bytes;
+        sv[j] = sk[j] + v_tile_off;
+        bar_e[j] = bar_empty + 8 * cst;
+        kbase[j] = key0 + (it0 + j) * TILE + 16 * gi;  // first key of this warp's group
+        if (++cst == p.stages) {
+          cst = 0;
+          cph ^= 1;
+        }
       }
 
+      if (p.debug & 1) {
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < NG; ++j) mbar_arrive(bar_e[j]);
+        }
+        return true;
+      }
+      // ---- S = K Q^T (16 keys x 8 heads per group), two accumulator chains each ----
+      float S[NG][4];
+#pragma unroll
+      for (int j = 0; j < NG; ++j) {
+        float Sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const uint32_t row_g = sk[j] + (16 * gi + g) * k_key_stride + kvh * k_head_stride;
+        const uint32_t row_h = row_g + 8 * k_key_stride;
+        if (!(p.debug & 4))
+        KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+          mma16816(Sc[n & 1], a0, a1, a2, a3, qb[n][0], qb[n][1]);
+        });
+#pragma unroll
+        for (int i = 0; i < 4; ++i) S[j][i] = Sc[0][i] + Sc[1][i];
+        if (kbase[j] + 15 > t_last) {  // tail tile: keys beyond the last attended one
+          if (kbase[j] + g > t_last) S[j][0] = S[j][1] = -INFINITY;
+          if (kbase[j] + g + 8 > t_last) S[j][2] = S[j][3] = -INFINITY;
+        }
+      }
+
+      uint32_t pb[NG][2];
+      if (p.debug & 16) {
+#pragma unroll
+        for (int j = 0; j < NG; ++j) pb[j][0] = pb[j][1] = __float_as_uint(S[j][0]) | 0x3c003c00u;
+      } else {
       // ---- online softmax (per head: columns 2t and 2t+1 of this lane) ----
-      float mx0 = fmaxf(S0, S2), mx1 = fmaxf(S1, S3);
+      float mx0 = fmaxf(S[0][0], S[0][2]), mx1 = fmaxf(S[0][1], S[0][3]);
+#pragma unroll
+      for (int j = 1; j < NG; ++j) {
+        mx0 = fmaxf(mx0, fmaxf(S[j][0], S[j][2]));
+        mx1 = fmaxf(mx1, fmaxf(S[j][1], S[j][3]));
+      }
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
         mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, o));
@@ -513,8 +580,7 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
       }
       if (__any_sync(FULL, mx0 > m0 || mx1 > m1)) {
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = ex2(m0 - (n0 == -INFINITY ? 0.f : n0));
-        const float c1 = ex2(m1 - (n1 == -INFINITY ? 0.f : n1));
+        const float c0 = ex2(m0 - n0), c1 = ex2(m1 - n1);
         m0 = n0;
         m1 = n1;
         l0 *= c0;
@@ -527,28 +593,46 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
           O[i][3] *= c1;
         }
       }
-      const float ms0 = m0 == -INFINITY ? 0.f : m0, ms1 = m1 == -INFINITY ? 0.f : m1;
-      const float p0 = ex2(S0 - ms0), p1 = ex2(S1 - ms1), p2 = ex2(S2 - ms0), p3 = ex2(S3 - ms1);
-      l0 += p0 + p2;
-      l1 += p1 + p3;
-      // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
-      const uint32_t pb0 = movmatrix_trans(pack_h2(p0, p1));
-      const uint32_t pb1 = movmatrix_trans(pack_h2(p2, p3));
+#pragma unroll
+      for (int j = 0; j < NG; ++j) {
+        const float p0 = ex2(S[j][0] - m0), p1 = ex2(S[j][1] - m1);
+        const float p2 = ex2(S[j][2] - m0), p3 = ex2(S[j][3] - m1);
+        l0 += p0 + p2;
+        l1 += p1 + p3;
+        // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
+        pb[j][0] = movmatrix_trans(pack_h2(p0, p1));
+        pb[j][1] = movmatrix_trans(pack_h2(p2, p3));
+      }
+      }
 
       // ---- O^T += V^T P^T (256 dims x 8 heads) ----
-      {
+#pragma unroll
+      for (int j = 0; j < NG; ++j) {
         uint32_t rows[4];
-        const uint32_t r0 = sv + (16 * gi + 2 * tq) * v_key_stride + kvh * v_head_stride;
+        const uint32_t r0 = sv[j] + (16 * gi + 2 * tq) * v_key_stride + kvh * v_head_stride;
         rows[0] = r0;
         rows[1] = r0 + v_key_stride;
         rows[2] = r0 + 8 * v_key_stride;
         rows[3] = r0 + 9 * v_key_stride;
+        if (!(p.debug & 8))
         VL::run(rows, g, [&](int m, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-          mma16816(O[m], a0, a1, a2, a3, pb0, pb1);
+          mma16816(O[m], a0, a1, a2, a3, pb[j][0], pb[j][1]);
         });
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < NG; ++j) mbar_arrive(bar_e[j]);
+      }
+      return true;
+    };
+    {
+      int it = 0;
+      bool ok = true;
+      if (KG < 3 && p.stages >= 2)  // two tiles per step only where registers allow
+        for (; ok && it + 1 < ntiles; it += 2) ok = step(std::integral_constant<int, 2>(), it);
+      for (; ok && it < ntiles; ++it) ok = step(std::integral_constant<int, 1>(), it);
+      if (!ok) s_abort = 1;
     }
     // row sums: add the 8 key-row lanes of each head column
 #pragma unroll
@@ -567,13 +651,18 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     }
   } else if (warp < CW) {
     // consumer warp without a (kv head, group) item: only keeps the ring moving
+    int st = 0;
+    uint32_t ph = 0;
     for (int it = 0; it < ntiles; ++it) {
-      const int st = it % p.stages;
-      if (!mbar_wait(bar_full + 8 * st, (it / p.stages) & 1, p.status, 3)) {
+      if (!mbar_wait(bar_full + 8 * st, ph, p.status, 3)) {
         s_abort = 1;
         break;
       }
       if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+      if (++st == p.stages) {
+        st = 0;
+        ph ^= 1;
+      }
     }
   }
 
@@ -584,58 +673,68 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     // bounded chance to land before the CTA (and its shared memory) goes away.
     if (threadIdx.x == 0) {
       for (int i = 0; i < p.stages && i < ntiles; ++i) {
-        const int last_it = ((ntiles - 1 - i) / p.stages) * p.stages + i;
-        mbar_wait(bar_full + 8 * i, (last_it / p.stages) & 1, nullptr, 0);
+        const int laps = (ntiles - 1 - i) / p.stages;  // last tile that used stage i
+        mbar_wait(bar_full + 8 * i, laps & 1, nullptr, 0);
       }
     }
     __syncthreads();
   }
-  float *stg = reinterpret_cast<float *>(smem + 16 * kMaxStages);  // [CW][6][kRec]
+  // Staging (aliases the tile ring): [warp][head][m, l, 8 blocks x 33 floats]; dim d of
+  // a head sits at 2 + 33*(d >> 5) + (d & 31), so the 8 row-lanes of a fragment (32 dims
+  // apart for the block loaders) hit 8 different banks.
+  float *stg = reinterpret_cast<float *>(smem + kRingOffset);
+  __shared__ float s_wgt[3][4 * kGroup];
+  if (p.debug & 64) return;
   if (active) {
-    float *mine = stg + (size_t)warp * kGroup * kRec;
+    float *mine = stg + (size_t)warp * kStgWarp;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int head = 2 * tq + hh;
       if (head < kGroup) {
-        float *rec = mine + head * kRec;
+        float *rec = mine + head * kStgHead;
         if (g == 0) {
-          rec[0] = hh ? m1 : m0;
+          const float mh = hh ? m1 : m0;
+          rec[0] = mh <= 0.5f * kNegBig ? -INFINITY : mh;  // no key seen: the empty record
           rec[1] = hh ? l1 : l0;
         }
 #pragma unroll
         for (int m = 0; m < 16; ++m) {
-          rec[2 + VL::dim(g, m, 0)] = O[m][hh];
-          rec[2 + VL::dim(g, m, 1)] = O[m][2 + hh];
+          const int d0 = VL::dim(g, m, 0), d1 = VL::dim(g, m, 1);
+          rec[2 + 33 * (d0 >> 5) + (d0 & 31)] = O[m][hh];
+          rec[2 + 33 * (d1 >> 5) + (d1 & 31)] = O[m][2 + hh];
         }
       }
     }
   }
   __syncthreads();
-  const int n_items = nkv * kGroup * kHeadDim;
-  for (int idx = threadIdx.x; idx < n_items; idx += blockDim.x) {
-    const int h = idx / kHeadDim, d = idx % kHeadDim;
-    const int hk = h / kGroup, hh = h % kGroup;
+  const int n_heads_cta = nkv * kGroup;
+  if ((int)threadIdx.x < n_heads_cta) {
+    // per head: weights of its key groups, and the record header
+    const int h = threadIdx.x, hk = h / kGroup, hh = h % kGroup;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < KG; ++w) mm = fmaxf(mm, stg[((w * nkv + hk) * kGroup + hh) * kRec]);
-    float acc = 0.f, ll = 0.f;
-    if (mm != -INFINITY && !s_abort) {
+    for (int w = 0; w < KG; ++w) mm = fmaxf(mm, stg[(w * nkv + hk) * kStgWarp + hh * kStgHead]);
+    float ll = 0.f;
 #pragma unroll
-      for (int w = 0; w < KG; ++w) {
-        const float *rec = stg + ((w * nkv + hk) * kGroup + hh) * kRec;
-        const float wgt = ex2(rec[0] - mm);
-        acc += rec[2 + d] * wgt;
-        ll += rec[1] * wgt;
-      }
-    } else {
-      mm = -INFINITY;
+    for (int w = 0; w < KG; ++w) {
+      const float *rec = stg + (w * nkv + hk) * kStgWarp + hh * kStgHead;
+      const float wgt = (mm == -INFINITY || s_abort) ? 0.f : ex2(rec[0] - mm);
+      s_wgt[w][h] = wgt;
+      ll += rec[1] * wgt;
     }
     float *out = p.partial + (((size_t)qt * p.n_head + h) * S + s) * kRec;
-    out[2 + d] = acc;
-    if (d == 0) {
-      out[0] = mm == -INFINITY ? -INFINITY : mm * 0.6931471805599453f;  // back to natural log
-      out[1] = ll;
-    }
+    out[0] = (mm == -INFINITY || s_abort) ? -INFINITY : mm * 0.6931471805599453f;  // natural log
+    out[1] = ll;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n_heads_cta * kHeadDim; idx += blockDim.x) {
+    const int h = idx >> 8, d = idx & 255;
+    const int hk = h / kGroup, hh = h % kGroup;
+    const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < KG; ++w) acc += stg[(w * nkv + hk) * kStgWarp + off] * s_wgt[w][h];
+    p.partial[(((size_t)qt * p.n_head + h) * S + s) * kRec + 2 + d] = acc;
   }
 }
 
@@ -646,11 +745,11 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   constexpr int TILE = 16 * KG;
   const int pitch = key_pitch(KT, a.n_head_kv) + key_pitch(VT, a.n_head_kv);
   const int stage_bytes = TILE * pitch;
-  int stages = (kSmemBudget - 16 * kMaxStages) / stage_bytes;
+  int stages = (kSmemBudget - kRingOffset) / stage_bytes;
   if (stages < 1) return RD_ERR_UNSUPPORTED;
   if (stages > kMaxStages) stages = kMaxStages;
-  size_t smem = 16 * kMaxStages + (size_t)stages * stage_bytes;
-  const size_t merge_bytes = 16 * kMaxStages + (size_t)4 * KG * kGroup * kRec * sizeof(float);
+  size_t smem = kRingOffset + (size_t)stages * stage_bytes;
+  const size_t merge_bytes = kRingOffset + (size_t)4 * KG * kStgWarp * sizeof(float);
   if (smem < merge_bytes) smem = merge_bytes;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   int dev = 0;
@@ -667,10 +766,10 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   }
   DecodeKernelArgs k;
   memset(&k, 0, sizeof(k));
-  // Quantized rows are small (144 / 272 bytes per kv head), so their tiles come in as
-  // one tensor-map copy per kv head; f16 / f32 rows are large enough for one plain bulk
-  // copy per key into the padded layout their loaders want. Tensor maps need the key
-  // count on the host, so launches that take it from a device array use bulk copies.
+  // Quantized keys are small (576 / 1088 bytes for 4 kv heads), so a whole tile comes in
+  // as one tensor-map copy; f16 / f32 keys are too wide for one box and large enough for
+  // one plain bulk copy per key. Tensor maps need the key count on the host, so
+  // launches that take it from a device array use bulk copies as well.
   const bool host_keys = a.pos == nullptr;
   const int64_t n_rows = (int64_t)a.t + 1;
   k.k_tmap = host_keys && n_rows > 0 && KT >= RD_KV_Q8_0 &&
@@ -688,6 +787,10 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.nkv = a.n_head_kv;
   k.qscale = a.scale * 1.4426950408889634f;
   k.stages = stages;
+  {
+    const char *e = getenv("RD_DECODE_DEBUG");
+    k.debug = e ? atoi(e) : 0;
+  }
   k.status = a.status;
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
   decode_kernel<KT, VT><<<grid, (4 * KG + 1) * 32, smem, st>>>(k);

@@ -44,9 +44,11 @@ int launch_decode(int kt, int vt, const DecodeArgs &a, cudaStream_t st);
 int decode_tile_keys(int kt, int vt);
 
 // ---- rd_tmap.cu
-// Tensor map over a KV cache viewed as u32 [n_rows][n_head_kv * row_bytes / 4] with a
-// box of [tile_rows][row_bytes / 4] (one kv head), no swizzle, zero fill outside.
-// Returns RD_OK, or an error if the driver entry point is unavailable or refuses.
+// Tensor map over a KV cache viewed as u64 [n_rows][key bytes / 8] with a box of
+// [tile_rows][key bytes / 8 + 2]: one copy brings a whole tile into shared memory with
+// a key pitch of key bytes + 16 (the extra columns are outside the tensor: zeros).
+// Returns RD_OK, or an error if the key is too wide for one box (f16 / f32 rows), the
+// driver entry point is unavailable, or the encoder refuses.
 int encode_kv_tmap(void *tmap_out, const void *base, int type, int n_head_kv, int64_t n_rows,
                    int tile_rows);
 

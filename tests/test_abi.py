@@ -89,3 +89,19 @@ def test_argument_validation_happens_on_the_host(rd):
     assert L.rd_fa2_prefill_usable(rd.F16, rd.F16, 512, 0, 24, 4, 128) == 0
     for code in range(-8, 1):
         assert rd.strerror(code) and "unknown" not in rd.strerror(code)
+
+
+def test_cpp_wrappers_compile_and_behave(rd, tmp_path):
+    """include/rdna4/ gives reference-named C++17 wrappers: a caller written against
+    the reference's names builds against them and links to the C-ABI library."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None or not os.path.isdir("/usr/local/cuda/include"):
+        pytest.skip("no host C++ toolchain / CUDA headers")
+    exe = str(tmp_path / "wrapper_check")
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror",
+                           "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include",
+                           os.path.join(ROOT, "tests", "cpp", "wrapper_check.cpp"), "-o", exe,
+                           "-L" + rd.HERE, "-lrd_attn_b200", "-Wl,-rpath," + rd.HERE])
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
