@@ -182,29 +182,28 @@ def main():
     for l in range(n_layers):
         rd.check(L.rd_kv_fill(KT, rd.ptr(kcache[l]), slice_rows * NKV, HD, 11 + 100 * l + rank, st))
         rd.check(L.rd_kv_fill(VT, rd.ptr(vcache[l]), slice_rows * NKV, HD, 22 + 100 * l + rank, st))
+    # One step's inputs (per layer: the query rows, the gate logits and the new K / V
+    # rows) live in ONE pinned host buffer and one device buffer, so that the end-to-end
+    # path is one host->device copy in and one device->host copy out per step.
     g = torch.Generator(device="cpu").manual_seed(0)
-    q_host = torch.randn(n_layers, NH, HD, generator=g).pin_memory()
-    gate_host = torch.randn(n_layers, NH, HD, generator=g).pin_memory()
-    knew_host = torch.randn(n_layers, NKV, HD, generator=g).pin_memory()
-    vnew_host = torch.randn(n_layers, NKV, HD, generator=g).pin_memory()
+    per_layer = 2 * NH * HD + 2 * NKV * HD
+    in_host = torch.randn(n_layers, per_layer, generator=g).pin_memory()
+    in_dev = in_host.cuda()
+    q_dev = [in_dev[l, :NH * HD].view(NH, HD) for l in range(n_layers)]
+    gate_dev = [in_dev[l, NH * HD:2 * NH * HD].view(NH, HD) for l in range(n_layers)]
+    knew_dev = [in_dev[l, 2 * NH * HD:2 * NH * HD + NKV * HD].view(NKV, HD) for l in range(n_layers)]
+    vnew_dev = [in_dev[l, 2 * NH * HD + NKV * HD:].view(NKV, HD) for l in range(n_layers)]
     out_host = torch.empty(n_layers, NH, HD).pin_memory()
-    q_dev, gate_dev = q_host.cuda(), gate_host.cuda()
-    knew_dev, vnew_dev = knew_host.cuda(), vnew_host.cuda()
     ws_bytes = L.rd_attn_workspace_bytes(1, NH, HD)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
     rec_mine = torch.empty(NH, 1, 2 + HD, device="cuda")
     rec_all = torch.empty(world, NH, 1, 2 + HD, device="cuda")
     rec_merge = torch.empty(NH, world, 2 + HD, device="cuda")
 
-    o_dev = torch.empty_like(q_dev)
+    o_dev = torch.empty(n_layers, NH, HD, device="cuda")
 
     def layer_step(l, host_io):
         st = rd.stream_ptr()   # the capturing stream while a graph is being recorded
-        if host_io:
-            q_dev[l].copy_(q_host[l], non_blocking=True)
-            gate_dev[l].copy_(gate_host[l], non_blocking=True)
-            knew_dev[l].copy_(knew_host[l], non_blocking=True)
-            vnew_dev[l].copy_(vnew_host[l], non_blocking=True)
         n = 0
         if owns_new_row:
             off = (POS - kb) * NKV * row
@@ -226,12 +225,15 @@ def main():
             rd.check(L.rd_attn_merge(rd.ptr(rec_merge), rd.ptr(o_dev[l]), NH, HD, world,
                                      rd.ptr(gate_dev[l]), st))
             n += 3
-        if host_io:
-            out_host[l].copy_(o_dev[l], non_blocking=True)
         return n
 
     def one_step(host_io):
-        return sum(layer_step(l, host_io) for l in range(n_layers))
+        if host_io:
+            in_dev.copy_(in_host, non_blocking=True)
+        n = sum(layer_step(l, host_io) for l in range(n_layers))
+        if host_io:
+            out_host.copy_(o_dev, non_blocking=True)
+        return n
 
     # One step (16 layers) is recorded into a CUDA graph and replayed: the per-launch
     # host cost of a Python caller would otherwise hide a ~30 us kernel. The device-
@@ -301,29 +303,34 @@ def main():
     tile = 32
     n_rec = min(sms, (slice_rows + tile - 1) // tile)
     rec = torch.empty(NH, n_rec, 2 + HD, device="cuda")
-    reps = 20 * n_layers
-
     def kernel_only(n):
+        stk = rd.stream_ptr()
         for i in range(n):
             l = i % n_layers
             rd.check(L.rd_attn_decode_split(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
-                                            rd.ptr(rec), slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, n_rec, st))
+                                            rd.ptr(rec), slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, n_rec, stk))
+    # graph replay, so that the host's launch rate cannot bound a ~30 us kernel
     kernel_only(n_layers)
     torch.cuda.synchronize()
+    kg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(kg):
+        kernel_only(n_layers)
+    kg.replay()
+    torch.cuda.synchronize()
+    reps = 20
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    kernel_only(reps)
+    for _ in range(reps):
+        kg.replay()
     e1.record()
     torch.cuda.synchronize()
-    k_ms = e0.elapsed_time(e1) / reps
+    k_ms = e0.elapsed_time(e1) / (reps * n_layers)
     k_bytes = algorithmic_bytes(slice_rows, row, row)
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
-    traffic = None
-    try:
-        prof = json.load(open(os.path.join(ROOT, "profiles", "decode_q4_0_traffic.json")))
-        traffic = prof["dram_bytes_per_key"] * slice_rows
-    except Exception:
-        pass
+    # dram__bytes_read + dram__bytes_write of one full-size launch (131001 keys), from the
+    # ncu capture summarised in profiles/decode_kernel_q4_0_131001keys.md; a context slice
+    # moves proportionally fewer bytes.
+    traffic = (150.99e6 + 6.83e6) * slice_rows / N_KEYS
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "decode_kernel<q4_0,q4_0>", "kernel_us": k_ms * 1e3,
                 "peak_source": peak_src, "frac_of_8tbs_nominal": achieved / 8000.0}
@@ -334,8 +341,7 @@ def main():
         "scaling": "strong", "vs_baseline": value / 63.0, "dtype": "f16 mma / f32 softmax+accumulate",
         "data": "synthetic", "config": workload_config(world),
         "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e / K,
-                "h2d_bytes_per_step": n_layers * (2 * NH * HD * 4 + 2 * NKV * HD * 4),
-                "d2h_bytes_per_step": n_layers * NH * HD * 4},
+                "h2d_bytes_per_step": in_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4},
         "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
         "us_per_layer": ms_dev / K / n_layers * 1e3,
     }
@@ -344,7 +350,7 @@ def main():
         ora = Oracle()
         kc = kcache[0].cpu().numpy()
         vc = vcache[0].cpu().numpy()
-        qn = q_host[0].numpy()
+        qn = in_host[0, :NH * HD].view(NH, HD).numpy()
         t0 = time.perf_counter()
         ora.attn(qn[None], kc, vc, [POS], NKV, SCALE, KT, VT)
         dt = time.perf_counter() - t0
