@@ -60,7 +60,8 @@ enum {
   RD_ERR_ALIGN = -5,       /* a pointer is not aligned as the entry point requires */
   RD_ERR_CUDA = -6,        /* a CUDA runtime call or launch failed */
   RD_ERR_WORKSPACE = -7,   /* caller-provided workspace too small / workspace growth failed */
-  RD_ERR_DEVICE = -8       /* a kernel recorded a bounded-wait timeout (rd_device_status) */
+  RD_ERR_DEVICE = -8,      /* a kernel recorded a bounded-wait timeout (rd_device_status) */
+  RD_ERR_LIMIT = -9        /* a size exceeds the fixed maximum of rd_attn_decode_noalloc */
 };
 
 const char *rd_strerror(int code);
@@ -136,6 +137,32 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
                       int key_begin, int t, int n_head, int n_head_kv, int head_dim, float scale,
                       int k_type, int v_type, int n_splits, float *gate, void *workspace,
                       size_t workspace_bytes, void *stream);
+
+/* ---- single-token attention that allocates nothing. (No counterpart in the reference.)
+ *
+ * Some hosts cannot let a library call cudaMalloc: a serving process whose memory
+ * manager has already claimed the whole device, a latency-critical decode loop in which
+ * the implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable,
+ * or an embedder with a no-allocation-after-start-up rule. For them this entry computes
+ * exactly what rd_attn_decode_split does (optionally with the fused sigmoid gate of
+ * rd_attn_decode_ws), but keeps its partial records in a fixed array that is part of
+ * the library image: RD_NOALLOC_MAX_HEADS x RD_NOALLOC_MAX_SPLITS records, 3.96 MB,
+ * resident on every GPU that loads the library until the process exits. It calls no
+ * cudaMalloc, no cudaFree and no allocating library routine.
+ *
+ *   - n_head above RD_NOALLOC_MAX_HEADS returns RD_ERR_LIMIT; the key split is capped at
+ *     RD_NOALLOC_MAX_SPLITS records per head (enough for one per SM on a B200).
+ *   - The first call on a device looks the array's device address up (once per device);
+ *     make that first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's
+ *     records. Nothing has to start at zero -- each call writes every record it later
+ *     merges -- but two calls whose kernels overlap on the GPU (different streams) race
+ *     on it. Calls on one stream are ordered and safe. */
+#define RD_NOALLOC_MAX_HEADS 24
+#define RD_NOALLOC_MAX_SPLITS 160
+int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *out, int t,
+                           int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                           int v_type, float *gate, void *stream);
 
 /* ---- merge: attn_merge_kernel / attn_merge_batch_kernel launches,
  * include/rdna4/attn.cuh:563-590,795-827. partial [n_rows][n_splits][2+head_dim],

@@ -21,8 +21,8 @@ F32, F16, Q8_0, Q4_0, Q5_0, Q4_1 = range(6)
 TYPE_NAMES = ("f32", "f16", "q8_0", "q4_0", "q5_0", "q4_1")
 
 OK = 0
-ERR_TYPE, ERR_SHAPE, ERR_UNSUPPORTED, ERR_NULL, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE = \
-    -1, -2, -3, -4, -5, -6, -7, -8
+ERR_TYPE, ERR_SHAPE, ERR_UNSUPPORTED, ERR_NULL, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE, \
+    ERR_LIMIT = -1, -2, -3, -4, -5, -6, -7, -8, -9
 
 # name -> (restype, argtypes); mirrors include/rd_attn.h one to one
 _P, _I, _F, _L = C.c_void_p, C.c_int, C.c_float, C.c_int64
@@ -45,6 +45,7 @@ SIGNATURES = {
     "rd_attn_decode_split": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P]),
     "rd_attn_decode_ws": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                C.c_size_t, _P]),
+    "rd_attn_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
     "rd_attn_merge": (_I, [_P, _P, _I, _I, _I, _P, _P]),
     "rd_attn_batch": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P]),
     "rd_attn_split_batch": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P]),

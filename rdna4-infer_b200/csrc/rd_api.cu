@@ -169,6 +169,27 @@ int attn_alloc(const float *q, const void *k, const void *v, float *out, float *
                    nullptr, ws, bytes, status_word(dev, true), sms, (cudaStream_t)stream);
 }
 
+// ---- allocation-free decode (rd_attn_decode_noalloc) --------------------------------
+// Partial records of the allocation-free entry point: part of the library image, so no
+// call ever has to allocate them. In host code the array's NAME is only a host-side
+// stand-in -- handing it to a kernel would pass a host address -- so the device address
+// is looked up once per device with cudaGetSymbolAddress and cached.
+constexpr size_t kNoAllocFloats =
+    (size_t)RD_NOALLOC_MAX_HEADS * RD_NOALLOC_MAX_SPLITS * kRec;
+static __device__ __align__(256) float g_noalloc_records[kNoAllocFloats];
+float *g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of the record array on the current device (dev); nullptr on failure.
+float *noalloc_records(int dev) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_records) != cudaSuccess) return nullptr;
+    g_noalloc_ptr[dev] = (float *)p;
+  }
+  return g_noalloc_ptr[dev];
+}
+
 }  // namespace
 
 extern "C" {
@@ -186,6 +207,7 @@ const char *rd_strerror(int code) {
     case RD_ERR_CUDA: return "CUDA runtime error";
     case RD_ERR_WORKSPACE: return "workspace missing or too small";
     case RD_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+    case RD_ERR_LIMIT: return "size beyond the fixed maximum of the allocation-free entry point";
   }
   return "unknown error code";
 }
@@ -341,6 +363,28 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
   return attn_core(q, k, v, out, partial, n_splits, nullptr, t, key_begin, 1, n_head, n_head_kv,
                    scale, k_type, v_type, gate, workspace, workspace_bytes, status_word(dev, false),
                    sm_count(dev), (cudaStream_t)stream);
+}
+
+int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *out, int t,
+                           int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                           int v_type, float *gate, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (n_head > RD_NOALLOC_MAX_HEADS) return RD_ERR_LIMIT;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return RD_ERR_NULL;
+  if (!aligned(q, 4) || !aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
+  if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  float *records = noalloc_records(dev);  // first call on this device: address look-up
+  if (records == nullptr) return RD_ERR_CUDA;
+  // Planning with at most RD_NOALLOC_MAX_SPLITS "SMs" caps the records per head, so the
+  // fixed array always holds them: n_head * splits * 258 floats <= kNoAllocFloats.
+  int sms = sm_count(dev);
+  if (sms > RD_NOALLOC_MAX_SPLITS) sms = RD_NOALLOC_MAX_SPLITS;
+  return attn_core(q, k, v, out, nullptr, 1, nullptr, t, 0, 1, n_head, n_head_kv, scale, k_type,
+                   v_type, gate, records, kNoAllocFloats * sizeof(float), status_word(dev, false),
+                   sms, (cudaStream_t)stream);
 }
 
 int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,

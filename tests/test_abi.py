@@ -87,7 +87,7 @@ def test_argument_validation_happens_on_the_host(rd):
     assert L.rd_fa2_prefill_usable(rd.F16, rd.F16, 512, 0, 24, 4, 256) == 1
     assert L.rd_fa2_prefill_usable(rd.Q8_0, rd.F16, 512, 0, 24, 4, 256) == 0
     assert L.rd_fa2_prefill_usable(rd.F16, rd.F16, 512, 0, 24, 4, 128) == 0
-    for code in range(-8, 1):
+    for code in range(-9, 1):
         assert rd.strerror(code) and "unknown" not in rd.strerror(code)
 
 
