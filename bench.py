@@ -358,9 +358,16 @@ def main():
                                "kind": "port", "sample": "one layer-step (131001 keys) of the same workload, "
                                "CPU oracle f32 attention, OpenMP over heads", "seconds": dt}
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a process group whose collectives
+        # were captured in CUDA graphs has been seen to block at exit. Everything is
+        # already synchronised and printed, so a hard exit loses nothing.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
