@@ -182,14 +182,26 @@ int rd_attn_split_batch(const float *q, const void *k, const void *v, float *out
                         float scale, int k_type, int v_type, int n_splits, void *stream);
 
 /* ---- causal prefill tile kernel: fa2_prefill_usable / fa2_prefill_launch,
- * include/rdna4/attn_fa2.cuh:174-207. f16/f16 caches. The admission window is wider
- * than the reference's (any n_q >= 1 and any key count), since the tensor-core
- * kernel has no measured-only range to protect. */
+ * include/rdna4/attn_fa2.cuh:174-207. f16/f16 caches; runs on tcgen05 tensor cores with
+ * TMEM accumulators. The admission window is wider than the reference's (any n_q >= 1
+ * and any key count), since the tensor-core kernel has no measured-only range to
+ * protect. keys_total rows must exist in the caches; token i attends keys 0..pos[i]. */
 int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head, int n_head_kv,
                           int head_dim);
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
                    int n_q, int kmax, int keys_total, int n_head, int n_head_kv, int head_dim,
                    float scale, void *stream);
+
+/* The same kernel with its fused edges (no single counterpart in the reference: it is
+ * rope_launch on q, include/rdna4/attn.cuh:56-63, + the prefill attention + the sigmoid
+ * gate of nn.cuh:405-420 in one launch). n_rot > 0 (a multiple of 16, <= 128) rotates
+ * the first n_rot dims of every query row by its pos[] on load -- q itself is not
+ * modified unless it aliases o; the K rows in the cache must already be rotated (use
+ * rd_kv_append with pos). gate != NULL multiplies the output by sigmoid(gate); the gate
+ * buffer is read only. q, o and gate must be 16-byte aligned. */
+int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o, const float *gate,
+                          const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
+                          int head_dim, float scale, int n_rot, float freq_base, void *stream);
 
 /* ---- device status: 0, or RD_ERR_DEVICE if any kernel launched through this
  * library on the current device gave up on a bounded wait since the last call.

@@ -51,6 +51,7 @@ SIGNATURES = {
     "rd_attn_split_batch": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P]),
     "rd_fa2_prefill_usable": (_I, [_I, _I, _I, _I, _I, _I, _I]),
     "rd_fa2_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
+    "rd_attn_prefill_fused": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _P]),
     "rd_device_status": (_I, []),
 }
 

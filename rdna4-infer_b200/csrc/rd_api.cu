@@ -422,13 +422,35 @@ int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head,
   return check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type) == RD_OK ? 1 : 0;
 }
 
+static int prefill_common(const float *q, const void *k, const void *v, float *o, const float *gate,
+                          const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
+                          int head_dim, float scale, int n_rot, float freq_base, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, RD_KV_F16, RD_KV_F16);
+  if (rc != RD_OK) return rc;
+  if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
+  if (n_rot < 0 || n_rot % 16 != 0 || n_rot > 128) return RD_ERR_SHAPE;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || pos == nullptr) return RD_ERR_NULL;
+  if (!aligned(q, 16) || !aligned(o, 16) || !aligned(gate, 16) || !aligned(pos, 4)) return RD_ERR_ALIGN;
+  if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  return launch_prefill(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, scale, n_rot,
+                        freq_base, status_word(dev, false), (cudaStream_t)stream);
+}
+
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
                    int n_q, int kmax, int keys_total, int n_head, int n_head_kv, int head_dim,
                    float scale, void *stream) {
-  if (n_q < 1 || kmax < 0 || keys_total <= 0) return RD_ERR_SHAPE;
-  if (o == nullptr || pos == nullptr) return RD_ERR_NULL;
-  return attn_alloc(q, k, v, o, nullptr, 1, pos, 0, n_q, n_head, n_head_kv, head_dim, scale,
-                    RD_KV_F16, RD_KV_F16, stream);
+  if (kmax < 0) return RD_ERR_SHAPE;
+  return prefill_common(q, k, v, o, nullptr, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
+                        0, 0.f, stream);
+}
+
+int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o, const float *gate,
+                          const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
+                          int head_dim, float scale, int n_rot, float freq_base, void *stream) {
+  return prefill_common(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
+                        n_rot, freq_base, stream);
 }
 
 int rd_device_status(void) {

@@ -52,6 +52,19 @@ int decode_tile_keys(int kt, int vt);
 int encode_kv_tmap(void *tmap_out, const void *base, int type, int n_head_kv, int64_t n_rows,
                    int tile_rows);
 
+// Tensor map over an f16 KV cache [n_rows][n_head_kv * 256] with a box of
+// [tile_rows][64 dims] and the hardware 128-byte swizzle (what tcgen05.mma descriptors
+// with SWIZZLE_128B read).
+int encode_f16_tmap(void *tmap_out, const void *base, int n_head_kv, int64_t n_rows, int tile_rows);
+
+// ---- rd_prefill.cu
+// Causal prefill attention over f16 caches on tcgen05: token i attends keys 0..pos[i]
+// (pos on the device), keys_total rows exist in the cache. gate (optional) fuses
+// out *= sigmoid(gate); n_rot > 0 applies the partial RoPE to the queries on load.
+int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
+                   const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
+                   int n_rot, float freq_base, DeviceStatus *status, cudaStream_t st);
+
 // ---- rd_merge.cu
 // partial [n_rows][n_splits][258] -> out [n_rows][256]; optional fused sigmoid gate.
 int launch_merge(const float *partial, float *out, int n_rows, int n_splits, float *gate,

@@ -1,0 +1,476 @@
+// Causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// Replaces attn_fa2_prefill_kernel (include/rdna4/attn_fa2.cuh:30-169 of the reference)
+// for f16 K/V caches. One CTA owns a tile of 128 query tokens of ONE query head:
+//
+//   prologue   the 128 x 256 f32 query rows -> f16, scaled by scale*log2(e), optional
+//              partial RoPE, written into shared memory in the K-major 128-byte-swizzled
+//              layout tcgen05.mma reads (4 sub-tiles of [128 rows][64 dims]);
+//   per 64-key tile j (2-stage TMA ring, K and V sub-tiles of [64 keys][64 dims],
+//              hardware 128B swizzle):
+//     MMA warp   S = Q K_j^T         16 x tcgen05.mma M128 N64  K16, accumulator in TMEM
+//     4 warps    thread r owns query row r = TMEM lane r: tcgen05.ld its 64 scores, causal
+//                mask (key <= pos[r]), running max with LAZY rescale (the reference point
+//                only moves when a row's max grows by more than 2^8, so P stays below 256
+//                in f16 and O in TMEM is rarely touched), P -> f16 into shared memory
+//     MMA warp   O += P V_j           4 x tcgen05.mma M128 N256 K16, V read MN-major
+//   epilogue   O / l (times sigmoid(gate) if asked) through a swizzled staging tile to
+//              coalesced f32 stores.
+//
+// Synchronisation is mbarriers only (TMA transaction counts, tcgen05.commit); every wait
+// is bounded and a timeout unwinds the CTA (TMEM is always freed). No cluster launch, no
+// multicast.
+#include <string.h>
+
+#include "rd_common.cuh"
+#include "rd_internal.h"
+
+namespace rd {
+
+constexpr int kPfM = 128;                 // query rows per CTA
+constexpr int kPfN = 64;                  // keys per tile
+constexpr int kPfStages = 2;
+constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536
+constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
+constexpr int kPfPBytes = kPfM * kPfN * 2;                 // 16384
+constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + kPfPBytes + 1024 /*align*/;
+constexpr int kPfThreads = 192;           // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemS = 0;            // columns [0, 64): scores
+constexpr uint32_t kTmemO = 64;           // columns [64, 320): output accumulator
+constexpr float kLazyThreshold = 8.0f;    // log2 units
+
+struct PrefillArgs {
+  alignas(64) CUtensorMap tm_k;
+  alignas(64) CUtensorMap tm_v;
+  const float *q;
+  float *out;
+  const float *gate;     // optional [n_q][n_head][256]
+  const int32_t *pos;    // device, one per query token
+  int n_q;
+  int n_head;
+  int nkv;
+  float qscale;          // scale * log2(e)
+  int n_rot;             // 0: the queries are already rotated
+  float freq_base;
+  DeviceStatus *status;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: f32 accumulate, f16 A and B.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+#define RD_LD64_REGS(r)                                                                         \
+  "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),  \
+  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),       \
+  "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),     \
+  "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),     \
+  "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+// 32 lanes x 32 consecutive columns: thread i gets lane base+i, registers = columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : RD_LD64_REGS(r)
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+      "%26,%27,%28,%29,%30,%31,%32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+// Same angle arithmetic as rope_kernel (rd_kv.cu): correctly rounded frequency, f32
+// product with the position, sin/cos of that f32 angle in double.
+__device__ __forceinline__ void rope_cs_dev(int pos, int p, int n_rot, float freq_base, float &c,
+                                            float &s) {
+  const float e = -2.0f * (float)p / (float)n_rot;
+  const float theta = (float)pos * (float)pow((double)freq_base, (double)e);
+  double sd, cd;
+  sincos((double)theta, &sd, &cd);
+  c = (float)cd;
+  s = (float)sd;
+}
+
+// Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
+enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 5, kBarCount = 6 };
+
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long s_bars[kBarCount];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_maxpos;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
+  const int head = blockIdx.y;
+  const int kvh = head / kGroup;
+  const int row0 = tile * kPfM;
+
+  // 1024-byte aligned carve-up of dynamic shared memory (128B swizzle atoms are 1 KB)
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base;
+  const uint32_t sKV = sQ + kPfQBytes;                    // stage s: K at +0, V at +32 KB
+  const uint32_t sP = sKV + kPfStages * kPfKVStageBytes;
+  uint8_t *gQ = smem_raw + (base - smem_u32(smem_raw));   // generic pointer to sQ
+  const uint32_t bars = smem_u32(s_bars);
+
+  if (threadIdx.x == 0) {
+    s_maxpos = -1;
+    s_abort = 0;
+    for (int i = 0; i < kPfStages; ++i) {
+      mbar_init(bars + 8 * (kBarKvFull + i), 1);
+      mbar_init(bars + 8 * (kBarKvFree + i), 1);
+    }
+    mbar_init(bars + 8 * kBarS, 1);
+    mbar_init(bars + 8 * kBarP, kPfM);
+    fence_barrier_init();
+  }
+  if (warp == 5) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  __syncthreads();
+
+  // ---- positions of this tile's rows; the last key any of them attends ----
+  int my_pos = -1;
+  if (threadIdx.x < kPfM) {
+    const int r = row0 + threadIdx.x;
+    if (r < p.n_q) my_pos = p.pos[r];
+    int mx = my_pos;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) atomicMax(&s_maxpos, mx);
+  }
+
+  // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-3) ----
+  if (warp < 4) {
+    for (int rr = 0; rr < 32; ++rr) {
+      const int r = warp * 32 + rr;      // row inside the tile
+      const int gr = row0 + r;
+      float v[8];
+      if (gr < p.n_q) {
+        const float4 *src =
+            reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim) + 2 * lane;
+        const float4 a = src[0], b = src[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      if (p.n_rot > 0) {
+        // lanes 0..(n_rot/8 - 1) hold the rotated dims; for n_rot == 64 dims p and p+32
+        // sit in lanes l and l^4 at the same element index
+        const int half_lanes = p.n_rot / 16;
+        const int rpos = gr < p.n_q ? p.pos[gr] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
+          if (lane < 2 * half_lanes) {
+            const bool lo = lane < half_lanes;
+            const int pr = 8 * (lo ? lane : lane - half_lanes) + i;
+            float c, s;
+            rope_cs_dev(rpos, pr, p.n_rot, p.freq_base, c, s);
+            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], c), __fmul_rn(other, s))
+                      : __fadd_rn(__fmul_rn(other, s), __fmul_rn(v[i], c));
+          }
+        }
+      }
+      const uint32_t w0 = pack_h2(v[0] * p.qscale, v[1] * p.qscale);
+      const uint32_t w1 = pack_h2(v[2] * p.qscale, v[3] * p.qscale);
+      const uint32_t w2 = pack_h2(v[4] * p.qscale, v[5] * p.qscale);
+      const uint32_t w3 = pack_h2(v[6] * p.qscale, v[7] * p.qscale);
+      // lane = 16-byte chunk of the row: sub-tile lane/8, chunk lane%8, swizzled by the row
+      const uint32_t dst = sQ + (lane >> 3) * (kPfM * 128) + r * 128 + (((lane & 7) ^ (r & 7)) << 4);
+      sts128(dst, w0, w1, w2, w3);
+    }
+    fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const int maxpos = s_maxpos;
+  const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
+
+  float l_run = 0.f;                 // softmax threads: row sum
+  float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
+
+  if (warp == 4) {
+    // =============================== TMA producer ==================================
+    if (lane == 0) {
+      for (int j = 0; j < nt; ++j) {
+        const int st = j & 1;
+        if (j >= kPfStages &&
+            !mbar_wait(bars + 8 * (kBarKvFree + st), ((j >> 1) - 1) & 1, p.status, 11)) {
+          s_abort = 1;
+          break;
+        }
+        if (*(volatile int *)&s_abort) break;
+        const uint32_t full = bars + 8 * (kBarKvFull + st);
+        mbar_expect_tx(full, kPfKVStageBytes);
+        const uint32_t sk = sKV + st * kPfKVStageBytes, sv = sk + kPfKVStageBytes / 2;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // four [64 keys][64 dims] sub-tiles per tensor
+          tma_load_2d(sk + c * (kPfN * 128), &p.tm_k, kvh * kHeadDim + 64 * c, j * kPfN, full);
+          tma_load_2d(sv + c * (kPfN * 128), &p.tm_v, kvh * kHeadDim + 64 * c, j * kPfN, full);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issuer ====================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_f16(kPfM, kPfN, false);
+      constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
+      for (int j = 0; j < nt; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(bars + 8 * (kBarKvFull + st), (j >> 1) & 1, p.status, 12)) {
+          s_abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sk = sKV + st * kPfKVStageBytes, sv = sk + kPfKVStageBytes / 2;
+        // S = Q K^T: K-major A and B, 16 steps of 16 dims; 8-row groups are 1 KB apart
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+          const uint64_t a = smem_desc(sQ + (kk >> 2) * (kPfM * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t b = smem_desc(sk + (kk >> 2) * (kPfN * 128) + (kk & 3) * 32, 16, 1024);
+          tc_mma_f16(tmem + kTmemS, a, b, idesc_s, kk > 0);
+        }
+        tc_commit(bars + 8 * kBarS);
+        // wait for P (and for the softmax threads to be done with S)
+        if (!mbar_wait(bars + 8 * kBarP, j & 1, p.status, 13)) {
+          s_abort = 1;
+          break;
+        }
+        tc_fence_after();
+        // O += P V: A = P K-major (keys), B = V MN-major: 64-dim groups 8 KB apart (LBO),
+        // 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t a = smem_desc(sP + kk * 32, 16, 1024);
+          const uint64_t b = smem_desc(sv + kk * 2048, kPfN * 128, 1024);
+          tc_mma_f16(tmem + kTmemO, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(bars + 8 * (kBarKvFree + st));  // stage reusable, O and P settled
+      }
+    }
+  } else {
+    // =============================== softmax (row = thread) ========================
+    const int r = threadIdx.x;
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    bool ok = true;
+    for (int j = 0; j < nt && ok; ++j) {
+      if (!mbar_wait(bars + 8 * kBarS, j & 1, p.status, 14)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sraw[2][32];
+      tmem_ld32(lane_addr + kTmemS, sraw[0]);
+      tmem_ld32(lane_addr + kTmemS + 32, sraw[1]);
+      tmem_wait_ld();
+      const int key0 = j * kPfN;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(sraw[h][i]);
+          if (key0 + 32 * h + i > my_pos) s = -INFINITY;  // causal / beyond the cache
+          sraw[h][i] = __float_as_uint(s);
+          mt = fmaxf(mt, s);
+        }
+      // previous P V must be complete before P is overwritten or O rescaled
+      if (j > 0 && !mbar_wait(bars + 8 * (kBarKvFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 15)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool grow = mt > m_ref + kLazyThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mt);
+        const float f = ex2(m_ref - m_new);   // 1 for rows that keep their reference
+        m_ref = m_new;
+        l_run *= f;
+        if (j > 0) {  // O holds data only after the first P V
+#pragma unroll 1
+          for (int c = 0; c < kHeadDim / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(lane_addr + kTmemO + 32 * c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st32(lane_addr + kTmemO + 32 * c, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // P = 2^(s - m_ref) as f16, row r of the K-major swizzled A tile
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {  // 8 keys = one 16-byte chunk
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = 8 * c + 2 * q;
+          const float p0 = ex2(__uint_as_float(sraw[i >> 5][i & 31]) - m_ref);
+          const float p1 = ex2(__uint_as_float(sraw[(i + 1) >> 5][(i + 1) & 31]) - m_ref);
+          lsum += p0 + p1;
+          w[q] = pack_h2(p0, p1);
+        }
+        sts128(sP + r * 128 + ((c ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+      }
+      l_run += lsum;
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * kBarP);
+    }
+    if (ok && nt > 0 &&
+        !mbar_wait(bars + 8 * (kBarKvFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
+      ok = false;
+    if (!ok) s_abort = 1;
+    tc_fence_after();
+  }
+
+  __syncthreads();
+  const bool aborted = s_abort != 0;
+
+  // ---- epilogue: O / l (x sigmoid(gate)) -> global, 64 columns at a time ----
+  // staging tile [128 rows][64 floats] aliases the Q region; 16-byte chunk q of row r is
+  // stored at q ^ (r & 15), so both the row-wise writes and the coalesced reads are
+  // conflict-free.
+  if (warp < 4) {
+    const int r = threadIdx.x;
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const float inv = (l_run > 0.f && !aborted) ? 1.0f / l_run : 0.f;
+    const bool have = nt > 0 && !aborted;
+    for (int c = 0; c < kHeadDim / 64; ++c) {
+      uint32_t o[2][32];
+      if (have) {
+        tmem_ld32(lane_addr + kTmemO + 64 * c, o[0]);
+        tmem_ld32(lane_addr + kTmemO + 64 * c + 32, o[1]);
+        tmem_wait_ld();
+      }
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const int hq = q >> 3, iq = (q & 7) * 4;
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          w[e] = have ? __float_as_uint(__uint_as_float(o[hq][iq + e]) * inv) : 0u;
+        sts128(sQ + r * 256 + ((q ^ (r & 15)) << 4), w[0], w[1], w[2], w[3]);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // 128 threads: 8 rows x 16 chunks per pass
+#pragma unroll 4
+      for (int pass = 0; pass < kPfM / 8; ++pass) {
+        const int rr = pass * 8 + (threadIdx.x >> 4), q = threadIdx.x & 15;
+        const int gr = row0 + rr;
+        if (gr < p.n_q) {
+          float4 v = *reinterpret_cast<const float4 *>(gQ + rr * 256 + ((q ^ (rr & 15)) << 4));
+          const size_t off = ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q;
+          if (p.gate != nullptr) {
+            const float4 g = *reinterpret_cast<const float4 *>(p.gate + off);
+            v.x *= __fdiv_rn(1.0f, 1.0f + expf(-g.x));
+            v.y *= __fdiv_rn(1.0f, 1.0f + expf(-g.y));
+            v.z *= __fdiv_rn(1.0f, 1.0f + expf(-g.z));
+            v.w *= __fdiv_rn(1.0f, 1.0f + expf(-g.w));
+          }
+          *reinterpret_cast<float4 *>(p.out + off) = v;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
+                   const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
+                   int n_rot, float freq_base, DeviceStatus *status, cudaStream_t st) {
+  PrefillArgs a;
+  memset(&a, 0, sizeof(a));
+  int rc = encode_f16_tmap(&a.tm_k, k, n_head_kv, keys_total, kPfN);
+  if (rc != RD_OK) return rc;
+  rc = encode_f16_tmap(&a.tm_v, v, n_head_kv, keys_total, kPfN);
+  if (rc != RD_OK) return rc;
+  a.q = q;
+  a.out = out;
+  a.gate = gate;
+  a.pos = pos;
+  a.n_q = n_q;
+  a.n_head = n_head;
+  a.nkv = n_head_kv;
+  a.qscale = scale * 1.4426950408889634f;
+  a.n_rot = n_rot;
+  a.freq_base = freq_base;
+  a.status = status;
+  static bool attr_set[32] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;
+  if (dev < 0 || dev >= 32 || !attr_set[dev]) {
+    if (cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kPfSmemBytes) != cudaSuccess)
+      return RD_ERR_CUDA;
+    if (dev >= 0 && dev < 32) attr_set[dev] = true;
+  }
+  const dim3 grid((unsigned)((n_q + kPfM - 1) / kPfM), (unsigned)n_head);
+  prefill_kernel<<<grid, kPfThreads, kPfSmemBytes, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+}  // namespace rd

@@ -49,4 +49,21 @@ int encode_kv_tmap(void *tmap_out, const void *base, int type, int n_head_kv, in
   return r == CUDA_SUCCESS ? RD_OK : RD_ERR_CUDA;
 }
 
+
+int encode_f16_tmap(void *tmap_out, const void *base, int n_head_kv, int64_t n_rows, int tile_rows) {
+  std::call_once(g_once, resolve);
+  if (g_encode == nullptr) return RD_ERR_CUDA;
+  if (n_rows < 1 || tile_rows > 256) return RD_ERR_SHAPE;
+  if (((uintptr_t)base & 15) != 0) return RD_ERR_ALIGN;
+  const cuuint64_t dims[2] = {(cuuint64_t)n_head_kv * kHeadDim, (cuuint64_t)n_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)n_head_kv * kHeadDim * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)tile_rows};  // 64 halves = one 128-byte swizzle row
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode((CUtensorMap *)tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                              const_cast<void *>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RD_OK : RD_ERR_CUDA;
+}
+
 }  // namespace rd

@@ -1,0 +1,100 @@
+"""Causal prefill attention (tcgen05 kernel) on the GPU against the CPU oracle and the
+golden vector of the reference's own tile kernel. Gates: max-abs <= 2e-3, cosine >= 0.9999."""
+import numpy as np
+import pytest
+
+from tests.conftest import check_attn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G(cuda):
+    from tests import gpu_util
+    return gpu_util
+
+
+def run_prefill(G, rd, q, kc, vc, pos, keys_total, nkv, gate=None, n_rot=0, inplace=False):
+    import torch
+    n_q, nh, _ = q.shape
+    dq, dk, dv, dpos = G.dev(q), G.dev(kc), G.dev(vc), G.dev(np.asarray(pos, dtype=np.int32))
+    out = dq if inplace else G.poison(q.shape)
+    dg = G.dev(gate) if gate is not None else None
+    if gate is None and n_rot == 0:
+        rc = rd.lib.rd_fa2_prefill(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), rd.ptr(dpos), n_q,
+                                   int(max(pos)), keys_total, nh, nkv, 256, 1 / 16, G.st())
+    else:
+        rc = rd.lib.rd_attn_prefill_fused(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), rd.ptr(dg),
+                                          rd.ptr(dpos), n_q, keys_total, nh, nkv, 256, 1 / 16, n_rot, 1e7,
+                                          G.st())
+    rd.check(rc, "prefill")
+    torch.cuda.synchronize()
+    assert rd.lib.rd_device_status() == rd.OK
+    return G.host(out)
+
+
+def test_golden_tile_kernel(G, golden, rd):
+    g = golden("fa2_prefill")
+    got = run_prefill(G, rd, g["q"], g["k"], g["v"], g["pos"], int(g["pos"][-1]) + 1, 1)
+    check_attn(got, g["out"], what="fa2 prefill golden")
+
+
+@pytest.mark.parametrize("n_q,pos0", [(512, 0), (200, 0), (128, 37), (1, 0), (512, 1536), (130, 4000)])
+def test_prefill_shapes_vs_oracle(G, oracle, rd, n_q, pos0):
+    rng = np.random.default_rng(n_q + pos0)
+    keys_total = pos0 + n_q
+    nh, nkv = (24, 4) if keys_total <= 1024 else (6, 1)   # keep the CPU oracle quick
+    K = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    V = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    q = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(1, K), oracle.kv_store_rows(1, V)
+    pos = np.arange(pos0, keys_total, dtype=np.int32)
+    want = oracle.attn(q, kc, vc, pos, nkv, 1 / 16, 1, 1)
+    got = run_prefill(G, rd, q, kc, vc, pos, keys_total, nkv)
+    check_attn(got, want, what=f"prefill n_q={n_q} pos0={pos0}")
+    got2 = run_prefill(G, rd, q, kc, vc, pos, keys_total, nkv, inplace=True)   # q and o alias
+    check_attn(got2, want, what="prefill in place")
+
+
+def test_prefill_ragged_positions_and_empty_rows(G, oracle, rd):
+    rng = np.random.default_rng(5)
+    keys_total, n_q = 300, 140
+    K = rng.standard_normal((keys_total, 1, 256)).astype(np.float32)
+    V = rng.standard_normal((keys_total, 1, 256)).astype(np.float32)
+    q = rng.standard_normal((n_q, 6, 256)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(1, K), oracle.kv_store_rows(1, V)
+    pos = rng.integers(0, keys_total, size=n_q).astype(np.int32)
+    pos[3] = -1            # a token with no keys: zeros
+    pos[77] = 0
+    want = oracle.attn(q, kc, vc, pos, 1, 1 / 16, 1, 1)
+    got = run_prefill(G, rd, q, kc, vc, pos, keys_total, 1)
+    assert (got[3] == 0).all()
+    check_attn(got, want, what="ragged pos")
+
+
+def test_prefill_fused_rope_and_gate(G, oracle, rd):
+    """BASELINE config 3 in one piece: 512 tokens at position 0, K/V appended as f16 with the
+    K RoPE fused into the append, Q RoPE and the sigmoid gate fused into the prefill."""
+    import torch
+    rng = np.random.default_rng(0)
+    n_q, nh, nkv = 512, 24, 4
+    q = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    ks = rng.standard_normal((n_q, nkv, 256)).astype(np.float32)
+    vs = rng.standard_normal((n_q, nkv, 256)).astype(np.float32)
+    gate = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    pos = np.arange(n_q, dtype=np.int32)
+    # oracle chain: rope(q), rope(k) -> f16 cache -> attention -> gate
+    qr, kr = oracle.rope(q, pos), oracle.rope(ks, pos)
+    kc_o, vc_o = oracle.kv_store_rows(1, kr), oracle.kv_store_rows(1, vs)
+    att = oracle.attn(qr, kc_o, vc_o, pos, nkv, 1 / 16, 1, 1)
+    _, want = oracle.sigmoid_gate(gate, att)
+    # device chain through the C ABI
+    dks, dvs, dpos = G.dev(ks), G.dev(vs), G.dev(pos)
+    kc = torch.zeros(n_q * nkv * 512, dtype=torch.uint8, device="cuda")
+    vc = torch.zeros_like(kc)
+    rd.check(rd.lib.rd_kv_append(1, 1, rd.ptr(dks), rd.ptr(dvs), rd.ptr(kc), rd.ptr(vc), n_q, nkv, 256,
+                                 rd.ptr(dpos), 64, 1e7, G.st()))
+    torch.cuda.synchronize()
+    assert (G.host(vc) == vc_o).all()
+    got = run_prefill(G, rd, q, G.host(kc), G.host(vc), pos, n_q, nkv, gate=gate, n_rot=64)
+    check_attn(got, want, what="fused rope + gate prefill-512")
