@@ -194,7 +194,7 @@ int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const
 
 /* The same kernel with its fused edges (no single counterpart in the reference: it is
  * rope_launch on q, include/rdna4/attn.cuh:56-63, + the prefill attention + the sigmoid
- * gate of nn.cuh:405-420 in one launch). n_rot > 0 (a multiple of 16, <= 128) rotates
+ * gate of nn.cuh:405-420 in one launch). n_rot > 0 (a multiple of 16, <= 64) rotates
  * the first n_rot dims of every query row by its pos[] on load -- q itself is not
  * modified unless it aliases o; the K rows in the cache must already be rotated (use
  * rd_kv_append with pos). gate != NULL multiplies the output by sigmoid(gate); the gate

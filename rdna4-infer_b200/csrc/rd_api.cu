@@ -428,7 +428,7 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, RD_KV_F16, RD_KV_F16);
   if (rc != RD_OK) return rc;
   if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
-  if (n_rot < 0 || n_rot % 16 != 0 || n_rot > 128) return RD_ERR_SHAPE;
+  if (n_rot < 0 || n_rot % 16 != 0 || n_rot > 64) return RD_ERR_SHAPE;
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || pos == nullptr) return RD_ERR_NULL;
   if (!aligned(q, 16) || !aligned(o, 16) || !aligned(gate, 16) || !aligned(pos, 4)) return RD_ERR_ALIGN;
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;

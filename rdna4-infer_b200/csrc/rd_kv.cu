@@ -106,12 +106,10 @@ __device__ __forceinline__ float rope_freq(float freq_base, int p, int n_rot) {
   const float e = -2.0f * (float)p / (float)n_rot;
   return (float)pow((double)freq_base, (double)e);
 }
-__device__ __forceinline__ void rope_cs(float theta, float &c, float &s) {
-  double sd, cd;
-  sincos((double)theta, &sd, &cd);
-  c = (float)cd;
-  s = (float)sd;
-}
+// sin/cos of the f32 angle with the accurate f32 routine (full-range argument
+// reduction, <= 2 ulp): what the reference's cosf/sinf do (attn.cuh:40-41), and far
+// cheaper than double for the 10^5..10^6 angles a prefill chunk needs.
+__device__ __forceinline__ void rope_cs(float theta, float &c, float &s) { sincosf(theta, &s, &c); }
 
 // One warp per 32-element block of K (blockIdx.y == 0) or V (blockIdx.y == 1).
 // With pos != nullptr the K value is rotated first (attn.cuh:30-54): element e of a

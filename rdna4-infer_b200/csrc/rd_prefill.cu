@@ -17,6 +17,9 @@
 //   epilogue   O / l (times sigmoid(gate) if asked) through a swizzled staging tile to
 //              coalesced f32 stores.
 //
+// Scores and P are double-buffered, so the tensor core computes S of tile j+1 while the
+// four softmax warps work on tile j, and P V of tile j while they wait for nothing else.
+//
 // Synchronisation is mbarriers only (TMA transaction counts, tcgen05.commit); every wait
 // is bounded and a timeout unwinds the CTA (TMEM is always freed). No cluster launch, no
 // multicast.
@@ -33,11 +36,11 @@ constexpr int kPfStages = 2;
 constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536
 constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
 constexpr int kPfPBytes = kPfM * kPfN * 2;                 // 16384
-constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + kPfPBytes + 1024 /*align*/;
+constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + 2 * kPfPBytes + 1024 /*align*/;
 constexpr int kPfThreads = 192;           // 4 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;            // columns [0, 64): scores
-constexpr uint32_t kTmemO = 64;           // columns [64, 320): output accumulator
+constexpr uint32_t kTmemS = 0;            // columns [0, 128): two score buffers of 64
+constexpr uint32_t kTmemO = 128;          // columns [128, 384): output accumulator
 constexpr float kLazyThreshold = 8.0f;    // log2 units
 
 struct PrefillArgs {
@@ -126,20 +129,14 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
                : "memory");
 }
 
-// Same angle arithmetic as rope_kernel (rd_kv.cu): correctly rounded frequency, f32
-// product with the position, sin/cos of that f32 angle in double.
-__device__ __forceinline__ void rope_cs_dev(int pos, int p, int n_rot, float freq_base, float &c,
-                                            float &s) {
+// RoPE frequency of pair p, correctly rounded (same arithmetic as rope_kernel, rd_kv.cu).
+__device__ __forceinline__ float rope_freq_dev(int p, int n_rot, float freq_base) {
   const float e = -2.0f * (float)p / (float)n_rot;
-  const float theta = (float)pos * (float)pow((double)freq_base, (double)e);
-  double sd, cd;
-  sincos((double)theta, &sd, &cd);
-  c = (float)cd;
-  s = (float)sd;
+  return (float)pow((double)freq_base, (double)e);
 }
 
 // Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
-enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 5, kBarCount = 6 };
+enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 6, kBarCount = 8 };
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -147,6 +144,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_maxpos;
   __shared__ int s_abort;
+  __shared__ float s_freq[64];  // RoPE frequencies of the n_rot/2 pairs
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
@@ -169,10 +167,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarKvFull + i), 1);
       mbar_init(bars + 8 * (kBarKvFree + i), 1);
     }
-    mbar_init(bars + 8 * kBarS, 1);
-    mbar_init(bars + 8 * kBarP, kPfM);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (kBarS + i), 1);
+      mbar_init(bars + 8 * (kBarP + i), kPfM);
+    }
     fence_barrier_init();
   }
+  if (p.n_rot > 0 && (int)threadIdx.x >= 64 && (int)threadIdx.x < 64 + p.n_rot / 2)
+    s_freq[threadIdx.x - 64] = rope_freq_dev(threadIdx.x - 64, p.n_rot, p.freq_base);
   if (warp == 5) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -195,6 +197,20 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 
   // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-3) ----
   if (warp < 4) {
+    // cos/sin of every (row, pair) of this warp's 32 rows, one row per lane, parked in the
+    // (still unused) P buffers: 32 rows x up to 64 pairs... n_rot <= 64 keeps it at 8 KB
+    float2 *cs_tab = reinterpret_cast<float2 *>(smem_raw + (sP - smem_u32(smem_raw))) + warp * (32 * 32);
+    const int pairs = p.n_rot / 2;
+    if (pairs > 0) {
+      const int gr_l = row0 + warp * 32 + lane;
+      const float fpos = gr_l < p.n_q ? (float)p.pos[gr_l] : 0.f;
+      for (int i = 0; i < pairs; ++i) {
+        float c, s;
+        sincosf(fpos * s_freq[i], &s, &c);
+        cs_tab[lane * 32 + i] = make_float2(c, s);
+      }
+      __syncwarp();
+    }
     for (int rr = 0; rr < 32; ++rr) {
       const int r = warp * 32 + rr;      // row inside the tile
       const int gr = row0 + r;
@@ -209,21 +225,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
       }
-      if (p.n_rot > 0) {
-        // lanes 0..(n_rot/8 - 1) hold the rotated dims; for n_rot == 64 dims p and p+32
-        // sit in lanes l and l^4 at the same element index
+      if (pairs > 0) {
+        // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
+        // l and l ^ (n_rot/16) at the same element index
         const int half_lanes = p.n_rot / 16;
-        const int rpos = gr < p.n_q ? p.pos[gr] : 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
           if (lane < 2 * half_lanes) {
             const bool lo = lane < half_lanes;
-            const int pr = 8 * (lo ? lane : lane - half_lanes) + i;
-            float c, s;
-            rope_cs_dev(rpos, pr, p.n_rot, p.freq_base, c, s);
-            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], c), __fmul_rn(other, s))
-                      : __fadd_rn(__fmul_rn(other, s), __fmul_rn(v[i], c));
+            const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
+            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
+                      : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
           }
         }
       }
@@ -273,38 +286,41 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kPfM, kPfN, false);
       constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
-      for (int j = 0; j < nt; ++j) {
+      // S(j) = Q K_j^T into score buffer j&1: K-major A and B, 16 steps of 16 dims,
+      // 8-row groups 1 KB apart
+      auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(bars + 8 * (kBarKvFull + st), (j >> 1) & 1, p.status, 12)) {
-          s_abort = 1;
-          break;
-        }
+        if (!mbar_wait(bars + 8 * (kBarKvFull + st), (j >> 1) & 1, p.status, 12)) return false;
         tc_fence_after();
-        const uint32_t sk = sKV + st * kPfKVStageBytes, sv = sk + kPfKVStageBytes / 2;
-        // S = Q K^T: K-major A and B, 16 steps of 16 dims; 8-row groups are 1 KB apart
+        const uint32_t sk = sKV + st * kPfKVStageBytes;
 #pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
           const uint64_t a = smem_desc(sQ + (kk >> 2) * (kPfM * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t b = smem_desc(sk + (kk >> 2) * (kPfN * 128) + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16(tmem + kTmemS, a, b, idesc_s, kk > 0);
+          tc_mma_f16(tmem + kTmemS + 64 * st, a, b, idesc_s, kk > 0);
         }
-        tc_commit(bars + 8 * kBarS);
-        // wait for P (and for the softmax threads to be done with S)
-        if (!mbar_wait(bars + 8 * kBarP, j & 1, p.status, 13)) {
-          s_abort = 1;
-          break;
-        }
+        tc_commit(bars + 8 * (kBarS + st));
+        return true;
+      };
+      bool ok = nt == 0 || issue_s(0);
+      for (int j = 0; j < nt && ok; ++j) {
+        const int st = j & 1;
+        // next tile's scores first: the softmax warps are still busy with tile j
+        if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
+        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) { ok = false; break; }
         tc_fence_after();
         // O += P V: A = P K-major (keys), B = V MN-major: 64-dim groups 8 KB apart (LBO),
         // 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
+        const uint32_t sv = sKV + st * kPfKVStageBytes + kPfKVStageBytes / 2;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t a = smem_desc(sP + kk * 32, 16, 1024);
+          const uint64_t a = smem_desc(sP + st * kPfPBytes + kk * 32, 16, 1024);
           const uint64_t b = smem_desc(sv + kk * 2048, kPfN * 128, 1024);
           tc_mma_f16(tmem + kTmemO, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bars + 8 * (kBarKvFree + st));  // stage reusable, O and P settled
+        tc_commit(bars + 8 * (kBarKvFree + st));  // stage and P buffer reusable, O settled
       }
+      if (!ok) s_abort = 1;
     }
   } else {
     // =============================== softmax (row = thread) ========================
@@ -312,36 +328,49 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
-      if (!mbar_wait(bars + 8 * kBarS, j & 1, p.status, 14)) { ok = false; break; }
+      const int st = j & 1;
+      if (!mbar_wait(bars + 8 * (kBarS + st), (j >> 1) & 1, p.status, 14)) { ok = false; break; }
       tc_fence_after();
       uint32_t sraw[2][32];
-      tmem_ld32(lane_addr + kTmemS, sraw[0]);
-      tmem_ld32(lane_addr + kTmemS + 32, sraw[1]);
+      tmem_ld32(lane_addr + kTmemS + 64 * st, sraw[0]);
+      tmem_ld32(lane_addr + kTmemS + 64 * st + 32, sraw[1]);
       tmem_wait_ld();
       const int key0 = j * kPfN;
       float mt = -INFINITY;
+      // only tiles that reach past some row's last key need the causal mask
+      if (__any_sync(0xffffffffu, key0 + kPfN - 1 > my_pos)) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(sraw[h][i]);
-          if (key0 + 32 * h + i > my_pos) s = -INFINITY;  // causal / beyond the cache
-          sraw[h][i] = __float_as_uint(s);
-          mt = fmaxf(mt, s);
-        }
-      // previous P V must be complete before P is overwritten or O rescaled
-      if (j > 0 && !mbar_wait(bars + 8 * (kBarKvFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 15)) {
+          for (int i = 0; i < 32; ++i)
+            if (key0 + 32 * h + i > my_pos) sraw[h][i] = 0xff800000u;  // -inf
+      }
+      {
+        // four independent chains: one warp per scheduler has nobody to hide latency behind
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[h][i]));
+        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      }
+      // the P buffer of this parity was last read by P V of tile j-2
+      if (j >= 2 && !mbar_wait(bars + 8 * (kBarKvFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
         ok = false;
         break;
       }
-      tc_fence_after();
       const bool grow = mt > m_ref + kLazyThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mt);
         const float f = ex2(m_ref - m_new);   // 1 for rows that keep their reference
         m_ref = m_new;
         l_run *= f;
-        if (j > 0) {  // O holds data only after the first P V
+        if (j > 0) {  // O holds data only after the first P V; and P V of tile j-1 must be done
+          if (!mbar_wait(bars + 8 * (kBarKvFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < kHeadDim / 32; ++c) {
             uint32_t o[32];
@@ -355,7 +384,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
       }
       // P = 2^(s - m_ref) as f16, row r of the K-major swizzled A tile
-      float lsum = 0.f;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t prow = sP + st * kPfPBytes + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {  // 8 keys = one 16-byte chunk
         uint32_t w[4];
@@ -364,15 +394,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           const int i = 8 * c + 2 * q;
           const float p0 = ex2(__uint_as_float(sraw[i >> 5][i & 31]) - m_ref);
           const float p1 = ex2(__uint_as_float(sraw[(i + 1) >> 5][(i + 1) & 31]) - m_ref);
-          lsum += p0 + p1;
+          ls[q] += p0 + p1;
           w[q] = pack_h2(p0, p1);
         }
-        sts128(sP + r * 128 + ((c ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        sts128(prow + ((c ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
       }
-      l_run += lsum;
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bars + 8 * kBarP);
+      mbar_arrive(bars + 8 * (kBarP + st));
     }
     if (ok && nt > 0 &&
         !mbar_wait(bars + 8 * (kBarKvFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
