@@ -136,7 +136,7 @@ __device__ __forceinline__ float rope_freq_dev(int p, int n_rot, float freq_base
 }
 
 // Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
-enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 6, kBarCount = 8 };
+enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 6, kBarQ = 8, kBarCount = 9 };
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarS + i), 1);
       mbar_init(bars + 8 * (kBarP + i), kPfM);
     }
+    mbar_init(bars + 8 * kBarQ, kPfM);
     fence_barrier_init();
   }
   if (p.n_rot > 0 && (int)threadIdx.x >= 64 && (int)threadIdx.x < 64 + p.n_rot / 2)
@@ -194,6 +195,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) atomicMax(&s_maxpos, mx);
   }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const int maxpos = s_maxpos;
+  const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
 
   // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-3) ----
   if (warp < 4) {
@@ -211,6 +218,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       }
       __syncwarp();
     }
+#pragma unroll 4
     for (int rr = 0; rr < 32; ++rr) {
       const int r = warp * 32 + rr;      // row inside the tile
       const int gr = row0 + r;
@@ -249,13 +257,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       sts128(dst, w0, w1, w2, w3);
     }
     fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+    mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 128 rows; TMA already runs
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = s_tmem_base;
-  const int maxpos = s_maxpos;
-  const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
 
   float l_run = 0.f;                 // softmax threads: row sum
   float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
@@ -302,7 +305,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         tc_commit(bars + 8 * (kBarS + st));
         return true;
       };
-      bool ok = nt == 0 || issue_s(0);
+      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile written by warps 0-3
+      tc_fence_after();
+      ok = ok && (nt == 0 || issue_s(0));
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
         // next tile's scores first: the softmax warps are still busy with tile j
@@ -441,7 +446,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       // 128 threads: 8 rows x 16 chunks per pass
-#pragma unroll 4
+#pragma unroll 8
       for (int pass = 0; pass < kPfM / 8; ++pass) {
         const int rr = pass * 8 + (threadIdx.x >> 4), q = threadIdx.x & 15;
         const int gr = row0 + rr;
@@ -450,10 +455,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           const size_t off = ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q;
           if (p.gate != nullptr) {
             const float4 g = *reinterpret_cast<const float4 *>(p.gate + off);
-            v.x *= __fdiv_rn(1.0f, 1.0f + expf(-g.x));
-            v.y *= __fdiv_rn(1.0f, 1.0f + expf(-g.y));
-            v.z *= __fdiv_rn(1.0f, 1.0f + expf(-g.z));
-            v.w *= __fdiv_rn(1.0f, 1.0f + expf(-g.w));
+            // fast exp/divide: ~1e-6 relative, far inside the attention tolerance
+            v.x *= __fdividef(1.0f, 1.0f + __expf(-g.x));
+            v.y *= __fdividef(1.0f, 1.0f + __expf(-g.y));
+            v.z *= __fdividef(1.0f, 1.0f + __expf(-g.z));
+            v.w *= __fdividef(1.0f, 1.0f + __expf(-g.w));
           }
           *reinterpret_cast<float4 *>(p.out + off) = v;
         }
