@@ -133,6 +133,69 @@ def reference_arm(args):
     }))
 
 
+def prefill_leg(rd, torch, peaks):
+    """Secondary measurement (1 GPU): the causal prefill kernel on the tensor roofline.
+    BASELINE config 3 -- 512 new tokens at position 0, f16 K/V, one layer: K/V append with
+    the K RoPE fused, then prefill attention with the Q RoPE and the sigmoid gate fused --
+    and the reference's own FA2 admission window (512 queries over 2048..8192 keys).
+    TFLOP/s counts causal-useful flops 4*256*24*sum(pos+1); peak = measured bf16 burst."""
+    L = rd.lib
+    peak = peaks.get("bf16_tflops", 1590.0)
+    res = {"unit": "TFLOP/s", "peak": peak, "peak_source": "measured" if "bf16_tflops" in peaks else "fallback"}
+
+    def run(n_q, pos0, fused):
+        keys = pos0 + n_q
+        kc = torch.empty(keys * NKV * 512, dtype=torch.uint8, device="cuda")
+        vc = torch.empty_like(kc)
+        st = rd.stream_ptr()
+        rd.check(L.rd_kv_fill(1, rd.ptr(kc), keys * NKV, HD, 11, st))
+        rd.check(L.rd_kv_fill(1, rd.ptr(vc), keys * NKV, HD, 22, st))
+        q = torch.randn(n_q, NH, HD, device="cuda")
+        o = torch.empty_like(q)
+        gate = torch.randn_like(q)
+        ks = torch.randn(n_q, NKV, HD, device="cuda")
+        vs = torch.randn(n_q, NKV, HD, device="cuda")
+        pos = torch.arange(pos0, keys, dtype=torch.int32, device="cuda")
+        row = NKV * 512
+
+        def call():
+            s2 = rd.stream_ptr()
+            if fused:
+                rd.check(L.rd_kv_append(1, 1, rd.ptr(ks), rd.ptr(vs), rd.ptr(kc) + pos0 * row,
+                                        rd.ptr(vc) + pos0 * row, n_q, NKV, HD, rd.ptr(pos), 64, 1e7, s2))
+                rd.check(L.rd_attn_prefill_fused(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(gate),
+                                                 rd.ptr(pos), n_q, keys, NH, NKV, HD, SCALE, 64, 1e7, s2))
+            else:
+                rd.check(L.rd_fa2_prefill(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(pos), n_q,
+                                          keys - 1, keys, NH, NKV, HD, SCALE, s2))
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(10):
+                call()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 100 * 1e3
+        flops = 4 * HD * NH * sum(pos0 + t + 1 for t in range(n_q))
+        tf = flops / us / 1e6
+        return {"us": us, "tflops": tf, "frac": tf / peak, "gflop": flops / 1e9}
+
+    res["config3_prefill512_pos0_fused_append_rope_gate"] = run(512, 0, True)
+    res["prefill512_pos0_attention_only"] = run(512, 0, False)
+    for keys in (2048, 4096, 8192):
+        res[f"fa2_window_512q_{keys}keys"] = run(512, keys - 512, False)
+    res["causal_8192x8192"] = run(8192, 0, False)
+    return res
+
+
 def workload_config(n_gpus):
     return {"workload": "decode q_len=1, ctx 131072 (pos 131000 -> 131001 keys), 24Q/4KV heads, hd 256, "
                         "K,V q4_0, 16 layer caches per step",
@@ -149,6 +212,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--leg", default="all", choices=["all", "prefill"], help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -159,6 +223,14 @@ def main():
 
     rd = importlib.import_module("rdna4-infer_b200")
     L = rd.lib
+    if args.leg == "prefill":   # profiling aid: only the prefill measurements
+        torch.cuda.set_device(0)
+        try:
+            pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pk = {}
+        print(json.dumps({"prefill": prefill_leg(rd, torch, pk)}))
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -345,6 +417,8 @@ def main():
         "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
         "us_per_layer": ms_dev / K / n_layers * 1e3,
     }
+    if rank == 0 and world == 1:
+        out["prefill"] = prefill_leg(rd, torch, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle.oracle import Oracle
         ora = Oracle()
