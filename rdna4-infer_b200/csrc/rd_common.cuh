@@ -153,8 +153,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after kWaitLimit polls, records the site in `status` and
 // returns false so the caller can unwind without leaving the GPU spinning.
 constexpr uint32_t kWaitLimit = 4u << 20;
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, DeviceStatus *status,
                                           int site) {
+  // a short burst of non-suspending polls first: most waits in a running pipeline are
+  // satisfied within a few hundred cycles, and try_wait may park the thread for longer
+  for (int i = 0; i < 128; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+  }
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }

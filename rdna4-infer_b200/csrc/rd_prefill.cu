@@ -9,7 +9,8 @@
 //   per 64-key tile j (2-stage TMA ring, K and V sub-tiles of [64 keys][64 dims],
 //              hardware 128B swizzle):
 //     MMA warp   S = Q K_j^T         16 x tcgen05.mma M128 N64  K16, accumulator in TMEM
-//     4 warps    thread r owns query row r = TMEM lane r: tcgen05.ld its 64 scores, causal
+//     8 warps    two threads per query row (= TMEM lane), 32 score columns each (row max
+//                exchanged through shared memory): tcgen05.ld the scores, causal
 //                mask (key <= pos[r]), running max with LAZY rescale (the reference point
 //                only moves when a row's max grows by more than 2^8, so P stays below 256
 //                in f16 and O in TMEM is rarely touched), P -> f16 into shared memory
@@ -23,6 +24,7 @@
 // Synchronisation is mbarriers only (TMA transaction counts, tcgen05.commit); every wait
 // is bounded and a timeout unwinds the CTA (TMEM is always freed). No cluster launch, no
 // multicast.
+#include <stdlib.h>
 #include <string.h>
 
 #include "rd_common.cuh"
@@ -36,8 +38,9 @@ constexpr int kPfStages = 2;
 constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536
 constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
 constexpr int kPfPBytes = kPfM * kPfN * 2;                 // 16384
-constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + 2 * kPfPBytes + 1024 /*align*/;
-constexpr int kPfThreads = 192;           // 4 softmax warps, 1 TMA warp, 1 MMA warp
+// 224 KB of dynamic shared memory + < 3 KB static = the 227 KB an sm_100 CTA may use
+constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + 2 * kPfPBytes;
+constexpr int kPfThreads = 320;           // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemS = 0;            // columns [0, 128): two score buffers of 64
 constexpr uint32_t kTmemO = 128;          // columns [128, 384): output accumulator
@@ -56,6 +59,7 @@ struct PrefillArgs {
   float qscale;          // scale * log2(e)
   int n_rot;             // 0: the queries are already rotated
   float freq_base;
+  int debug;             // timing experiments only (bit mask), 0 in production
   DeviceStatus *status;
 };
 
@@ -136,15 +140,19 @@ __device__ __forceinline__ float rope_freq_dev(int p, int n_rot, float freq_base
 }
 
 // Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
-enum { kBarKvFull = 0, kBarKvFree = 2, kBarS = 4, kBarP = 6, kBarQ = 8, kBarCount = 9 };
+// K and V tiles travel on separate rings: a K stage is free as soon as its S MMAs are
+// done (long before the tile's P V), so K loads run two tiles ahead.
+enum { kBarVFull = 0, kBarVFree = 2, kBarS = 4, kBarP = 6, kBarQ = 8, kBarKFull = 9, kBarKFree = 11,
+       kBarX = 13, kBarCount = 15 };
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) unsigned long long s_bars[kBarCount];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_maxpos;
   __shared__ int s_abort;
   __shared__ float s_freq[64];  // RoPE frequencies of the n_rot/2 pairs
+  __shared__ float s_mx[2][2][kPfM];   // [tile parity][column half][row]: partial row maxima
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
@@ -152,8 +160,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   const int kvh = head / kGroup;
   const int row0 = tile * kPfM;
 
-  // 1024-byte aligned carve-up of dynamic shared memory (128B swizzle atoms are 1 KB)
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // carve-up of dynamic shared memory; 128B-swizzle atoms need the base 1 KB aligned
+  const uint32_t base = smem_u32(smem_raw);
+  if ((base & 1023u) != 0) {  // cannot happen with the declared alignment; refuse, do not corrupt
+    if (threadIdx.x == 0 && p.status != nullptr && atomicExch(&p.status->timeout_flag, 1) == 0)
+      p.status->where = 99;
+    return;
+  }
   const uint32_t sQ = base;
   const uint32_t sKV = sQ + kPfQBytes;                    // stage s: K at +0, V at +32 KB
   const uint32_t sP = sKV + kPfStages * kPfKVStageBytes;
@@ -164,19 +177,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     s_maxpos = -1;
     s_abort = 0;
     for (int i = 0; i < kPfStages; ++i) {
-      mbar_init(bars + 8 * (kBarKvFull + i), 1);
-      mbar_init(bars + 8 * (kBarKvFree + i), 1);
+      mbar_init(bars + 8 * (kBarVFull + i), 1);
+      mbar_init(bars + 8 * (kBarVFree + i), 1);
+      mbar_init(bars + 8 * (kBarKFull + i), 1);
+      mbar_init(bars + 8 * (kBarKFree + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + 8 * (kBarS + i), 1);
-      mbar_init(bars + 8 * (kBarP + i), kPfM);
+      mbar_init(bars + 8 * (kBarP + i), 8);   // one elected lane per softmax warp
+      mbar_init(bars + 8 * (kBarX + i), 8);
     }
-    mbar_init(bars + 8 * kBarQ, kPfM);
+    mbar_init(bars + 8 * kBarQ, 4);          // one per prologue warp
     fence_barrier_init();
   }
   if (p.n_rot > 0 && (int)threadIdx.x >= 64 && (int)threadIdx.x < 64 + p.n_rot / 2)
     s_freq[threadIdx.x - 64] = rope_freq_dev(threadIdx.x - 64, p.n_rot, p.freq_base);
-  if (warp == 5) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
+  if (warp == 9) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
                  "r"(kTmemCols)
@@ -187,9 +203,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 
   // ---- positions of this tile's rows; the last key any of them attends ----
   int my_pos = -1;
-  if (threadIdx.x < kPfM) {
-    const int r = row0 + threadIdx.x;
+  if (threadIdx.x < 2 * kPfM) {
+    const int r = row0 + (threadIdx.x & (kPfM - 1));
     if (r < p.n_q) my_pos = p.pos[r];
+  }
+  if (threadIdx.x < kPfM) {
     int mx = my_pos;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -257,34 +275,40 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       sts128(dst, w0, w1, w2, w3);
     }
     fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
-    mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 128 rows; TMA already runs
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 4 warps; TMA already runs
   }
 
   float l_run = 0.f;                 // softmax threads: row sum
   float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
 
-  if (warp == 4) {
+  if (warp == 8) {
     // =============================== TMA producer ==================================
-    if (lane == 0) {
+    // lane 0 feeds the K ring, lane 1 the V ring (independent waits)
+    if (lane < 2) {
+      const bool is_k = lane == 0;
+      const CUtensorMap *tm = is_k ? &p.tm_k : &p.tm_v;
+      const int b_full = is_k ? kBarKFull : kBarVFull, b_free = is_k ? kBarKFree : kBarVFree;
       for (int j = 0; j < nt; ++j) {
         const int st = j & 1;
-        if (j >= kPfStages &&
-            !mbar_wait(bars + 8 * (kBarKvFree + st), ((j >> 1) - 1) & 1, p.status, 11)) {
+        if (j >= kPfStages && !mbar_wait(bars + 8 * (b_free + st), ((j >> 1) - 1) & 1, p.status, 11)) {
           s_abort = 1;
           break;
         }
         if (*(volatile int *)&s_abort) break;
-        const uint32_t full = bars + 8 * (kBarKvFull + st);
-        mbar_expect_tx(full, kPfKVStageBytes);
-        const uint32_t sk = sKV + st * kPfKVStageBytes, sv = sk + kPfKVStageBytes / 2;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {  // four [64 keys][64 dims] sub-tiles per tensor
-          tma_load_2d(sk + c * (kPfN * 128), &p.tm_k, kvh * kHeadDim + 64 * c, j * kPfN, full);
-          tma_load_2d(sv + c * (kPfN * 128), &p.tm_v, kvh * kHeadDim + 64 * c, j * kPfN, full);
+        const uint32_t full = bars + 8 * (b_full + st);
+        if (p.debug & 32) {
+          mbar_arrive(full);
+          continue;
         }
+        mbar_expect_tx(full, kPfKVStageBytes / 2);
+        const uint32_t dst = sKV + st * kPfKVStageBytes + (is_k ? 0 : kPfKVStageBytes / 2);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)  // four [64 keys][64 dims] sub-tiles
+          tma_load_2d(dst + c * (kPfN * 128), tm, kvh * kHeadDim + 64 * c, j * kPfN, full);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // =============================== MMA issuer ====================================
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kPfM, kPfN, false);
@@ -293,16 +317,17 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       // 8-row groups 1 KB apart
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(bars + 8 * (kBarKvFull + st), (j >> 1) & 1, p.status, 12)) return false;
+        if (!mbar_wait(bars + 8 * (kBarKFull + st), (j >> 1) & 1, p.status, 12)) return false;
         tc_fence_after();
         const uint32_t sk = sKV + st * kPfKVStageBytes;
 #pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
           const uint64_t a = smem_desc(sQ + (kk >> 2) * (kPfM * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t b = smem_desc(sk + (kk >> 2) * (kPfN * 128) + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16(tmem + kTmemS + 64 * st, a, b, idesc_s, kk > 0);
+          if (!(p.debug & 8)) tc_mma_f16(tmem + kTmemS + 64 * st, a, b, idesc_s, kk > 0);
         }
         tc_commit(bars + 8 * (kBarS + st));
+        tc_commit(bars + 8 * (kBarKFree + st));  // the K stage can be refilled
         return true;
       };
       bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile written by warps 0-3
@@ -312,7 +337,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         const int st = j & 1;
         // next tile's scores first: the softmax warps are still busy with tile j
         if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) { ok = false; break; }
+        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13) ||
+            !mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
         // O += P V: A = P K-major (keys), B = V MN-major: 64-dim groups 8 KB apart (LBO),
         // 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
@@ -321,46 +350,46 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t a = smem_desc(sP + st * kPfPBytes + kk * 32, 16, 1024);
           const uint64_t b = smem_desc(sv + kk * 2048, kPfN * 128, 1024);
-          tc_mma_f16(tmem + kTmemO, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          if (!(p.debug & 4)) tc_mma_f16(tmem + kTmemO, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bars + 8 * (kBarKvFree + st));  // stage and P buffer reusable, O settled
+        tc_commit(bars + 8 * (kBarVFree + st));  // stage and P buffer reusable, O settled
       }
       if (!ok) s_abort = 1;
     }
   } else {
-    // =============================== softmax (row = thread) ========================
-    const int r = threadIdx.x;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    // ================== softmax: thread = (row r, 32-column half ch) ==================
+    const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
       const int st = j & 1;
       if (!mbar_wait(bars + 8 * (kBarS + st), (j >> 1) & 1, p.status, 14)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sraw[2][32];
-      tmem_ld32(lane_addr + kTmemS + 64 * st, sraw[0]);
-      tmem_ld32(lane_addr + kTmemS + 64 * st + 32, sraw[1]);
+      uint32_t sraw[32];
+      tmem_ld32(lane_addr + kTmemS + 64 * st + 32 * ch, sraw);
       tmem_wait_ld();
-      const int key0 = j * kPfN;
-      float mt = -INFINITY;
+      const int key0 = j * kPfN + 32 * ch;
       // only tiles that reach past some row's last key need the causal mask
-      if (__any_sync(0xffffffffu, key0 + kPfN - 1 > my_pos)) {
+      if (__any_sync(0xffffffffu, key0 + 31 > my_pos)) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (key0 + 32 * h + i > my_pos) sraw[h][i] = 0xff800000u;  // -inf
+        for (int i = 0; i < 32; ++i)
+          if (key0 + i > my_pos) sraw[i] = 0xff800000u;  // -inf
       }
-      {
-        // four independent chains: one warp per scheduler has nobody to hide latency behind
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[h][i]));
-        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[i]));
+      float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      s_mx[st][ch][r] = mt;
+      // exchange through an mbarrier (bounded wait) rather than bar.sync: a thread that
+      // gave up on a wait must not leave the others parked on a hardware barrier
+      if (!(p.debug & 16)) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kBarX + st));
+      if (!mbar_wait(bars + 8 * (kBarX + st), (j >> 1) & 1, p.status, 20)) { ok = false; break; }
       }
+      mt = fmaxf(mt, s_mx[st][ch ^ 1][r]);   // both halves now agree on the row maximum
       // the P buffer of this parity was last read by P V of tile j-2
-      if (j >= 2 && !mbar_wait(bars + 8 * (kBarKvFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
+      if (j >= 2 && !mbar_wait(bars + 8 * (kBarVFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
         ok = false;
         break;
       }
@@ -371,46 +400,48 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         m_ref = m_new;
         l_run *= f;
         if (j > 0) {  // O holds data only after the first P V; and P V of tile j-1 must be done
-          if (!mbar_wait(bars + 8 * (kBarKvFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
+          if (!mbar_wait(bars + 8 * (kBarVFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
             ok = false;
             break;
           }
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < kHeadDim / 32; ++c) {
+          for (int c = 0; c < kHeadDim / 64; ++c) {   // this half's 128 output columns
             uint32_t o[32];
-            tmem_ld32(lane_addr + kTmemO + 32 * c, o);
+            const uint32_t col = kTmemO + 128 * ch + 32 * c;
+            tmem_ld32(lane_addr + col, o);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st32(lane_addr + kTmemO + 32 * c, o);
+            tmem_st32(lane_addr + col, o);
           }
           tmem_wait_st();
         }
       }
-      // P = 2^(s - m_ref) as f16, row r of the K-major swizzled A tile
+      // P = 2^(s - m_ref) as f16: chunks 4ch..4ch+3 of row r of the K-major swizzled A tile
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       const uint32_t prow = sP + st * kPfPBytes + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {  // 8 keys = one 16-byte chunk
+      for (int c = 0; c < 4; ++c) {  // 8 keys = one 16-byte chunk
         uint32_t w[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int i = 8 * c + 2 * q;
-          const float p0 = ex2(__uint_as_float(sraw[i >> 5][i & 31]) - m_ref);
-          const float p1 = ex2(__uint_as_float(sraw[(i + 1) >> 5][(i + 1) & 31]) - m_ref);
+          const float p0 = (p.debug & 1) ? __uint_as_float(sraw[i]) : ex2(__uint_as_float(sraw[i]) - m_ref);
+          const float p1 = (p.debug & 1) ? __uint_as_float(sraw[i + 1]) : ex2(__uint_as_float(sraw[i + 1]) - m_ref);
           ls[q] += p0 + p1;
           w[q] = pack_h2(p0, p1);
         }
-        sts128(prow + ((c ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        sts128(prow + (((4 * ch + c) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      fence_proxy_async();
+      if (!(p.debug & 2)) fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bars + 8 * (kBarP + st));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kBarP + st));
     }
     if (ok && nt > 0 &&
-        !mbar_wait(bars + 8 * (kBarKvFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
+        !mbar_wait(bars + 8 * (kBarVFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
       ok = false;
     if (!ok) s_abort = 1;
     tc_fence_after();
@@ -418,17 +449,26 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 
   __syncthreads();
   const bool aborted = s_abort != 0;
+  // the two column halves of a row add their partial sums (s_mx is free now)
+  if (warp < 8) s_mx[0][threadIdx.x >> 7][threadIdx.x & (kPfM - 1)] = l_run;
+  __syncthreads();
 
   // ---- epilogue: O / l (x sigmoid(gate)) -> global, 64 columns at a time ----
   // staging tile [128 rows][64 floats] aliases the Q region; 16-byte chunk q of row r is
   // stored at q ^ (r & 15), so both the row-wise writes and the coalesced reads are
   // conflict-free.
-  if (warp < 4) {
-    const int r = threadIdx.x;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    const float inv = (l_run > 0.f && !aborted) ? 1.0f / l_run : 0.f;
+  if (warp < 8) {
+    // warpgroup ch stores output columns [64*(2c+ch), +64), c = 0..1, through its own
+    // staging tile and named barrier
+    const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7, gt = threadIdx.x & (kPfM - 1);
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const float l_tot = s_mx[0][0][r] + s_mx[0][1][r];
+    const float inv = (l_tot > 0.f && !aborted) ? 1.0f / l_tot : 0.f;
     const bool have = nt > 0 && !aborted;
-    for (int c = 0; c < kHeadDim / 64; ++c) {
+    const uint32_t stg = sQ + ch * (kPfM * 256);
+    uint8_t *gstg = gQ + ch * (kPfM * 256);
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = 2 * cc + ch;
       uint32_t o[2][32];
       if (have) {
         tmem_ld32(lane_addr + kTmemO + 64 * c, o[0]);
@@ -442,16 +482,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           w[e] = have ? __float_as_uint(__uint_as_float(o[hq][iq + e]) * inv) : 0u;
-        sts128(sQ + r * 256 + ((q ^ (r & 15)) << 4), w[0], w[1], w[2], w[3]);
+        sts128(stg + r * 256 + ((q ^ (r & 15)) << 4), w[0], w[1], w[2], w[3]);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
       // 128 threads: 8 rows x 16 chunks per pass
 #pragma unroll 8
       for (int pass = 0; pass < kPfM / 8; ++pass) {
-        const int rr = pass * 8 + (threadIdx.x >> 4), q = threadIdx.x & 15;
+        const int rr = pass * 8 + (gt >> 4), q = gt & 15;
         const int gr = row0 + rr;
         if (gr < p.n_q) {
-          float4 v = *reinterpret_cast<const float4 *>(gQ + rr * 256 + ((q ^ (rr & 15)) << 4));
+          float4 v = *reinterpret_cast<const float4 *>(gstg + rr * 256 + ((q ^ (rr & 15)) << 4));
           const size_t off = ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q;
           if (p.gate != nullptr) {
             const float4 g = *reinterpret_cast<const float4 *>(p.gate + off);
@@ -464,12 +504,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           *reinterpret_cast<float4 *>(p.out + off) = v;
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");
   }
@@ -495,6 +535,10 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   a.n_rot = n_rot;
   a.freq_base = freq_base;
   a.status = status;
+  {
+    const char *e = getenv("RD_PREFILL_DEBUG");
+    a.debug = e ? atoi(e) : 0;
+  }
   static bool attr_set[32] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;
