@@ -22,11 +22,14 @@ cpu_baseline: the CPU oracle's attention (all host threads) on one layer of the 
 workload.
 
 With N > 1 (one process per GPU under torch.distributed.run) the context is sharded:
-rank r holds keys [r*ceil(n/N), ...) of every layer, computes one partial record per
-head, the records are all-gathered over NCCL and merged on every rank ("strong"
-scaling: the job is fixed, the per-GPU slice shrinks).
+rank r holds keys [r*ceil(n/N), ...) of every layer and computes one partial record per
+head; the library's exchange kernels store that record into every rank's peer-mapped
+buffer and merge once all have arrived (an NCCL all-gather between two merges is the
+fallback when the peer mapping cannot be set up). "strong" scaling: the job is fixed,
+the per-GPU slice shrinks.
 """
 import argparse
+import ctypes
 import importlib
 import json
 import math
@@ -200,7 +203,7 @@ def workload_config(n_gpus):
     return {"workload": "decode q_len=1, ctx 131072 (pos 131000 -> 131001 keys), 24Q/4KV heads, hd 256, "
                         "K,V q4_0, 16 layer caches per step",
             "l2": "16 distinct 151 MB cache pairs walked per step (> 126 MB L2)",
-            "parallelism": f"context sharded over {n_gpus} GPU(s), NCCL all-gather of partial records"
+            "parallelism": f"context sharded over {n_gpus} GPU(s), one record per head exchanged per layer"
             if n_gpus > 1 else "1 GPU"}
 
 
@@ -232,6 +235,8 @@ def main():
         print(json.dumps({"prefill": prefill_leg(rd, torch, pk)}))
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"    # NCCL prints its version banner to stdout otherwise
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -271,6 +276,34 @@ def main():
     rec_mine = torch.empty(NH, 1, 2 + HD, device="cuda")
     rec_all = torch.empty(world, NH, 1, 2 + HD, device="cuda")
     rec_merge = torch.empty(NH, world, 2 + HD, device="cuda")
+    # N > 1: the ranks exchange one record per head and layer. Preferred: the library's
+    # fused exchange (peer stores into every rank's buffer + flags, no collective call),
+    # over buffers mapped into every process by torch's symmetric memory. If that
+    # mapping cannot be set up, the exchange is an NCCL all-gather between two merges.
+    group = None
+    exchange = "none (1 GPU)"
+    if world > 1:
+        exchange = "nccl all_gather of records"
+        if os.environ.get("RD_BENCH_EXCHANGE", "peer") == "peer":
+            try:
+                import torch.distributed._symmetric_memory as symm
+                xbytes = L.rd_shard_xbuf_bytes(NH, HD, world)
+                xbuf = symm.empty(xbytes, dtype=torch.uint8, device=torch.device("cuda", local))
+                hdl = symm.rendezvous(xbuf, dist.group.WORLD)
+                xbuf.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                group = rd.shard_group(rank, [int(p) for p in hdl.buffer_ptrs])
+                group._tensor, group._handle = xbuf, hdl
+                exchange = "peer stores + flags (fused into the merge kernels)"
+            except Exception as e:
+                if rank == 0:
+                    print(f"# symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                group = None
+        ok = torch.tensor([1 if group is not None else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)     # all ranks take the same path
+        if int(ok.item()) == 0:
+            group, exchange = None, "nccl all_gather of records"
 
     o_dev = torch.empty(n_layers, NH, HD, device="cuda")
 
@@ -288,6 +321,12 @@ def main():
                                          rd.ptr(o_dev[l]), None, 0, POS, NH, NKV, HD, SCALE, KT, VT, 16,
                                          rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes, st))
             n += 2
+        elif group is not None:
+            rd.check(L.rd_attn_decode_sharded(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]),
+                                              rd.ptr(o_dev[l]), slice_rows - 1, NH, NKV, HD, SCALE, KT, VT,
+                                              rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
+                                              ctypes.addressof(group), st))
+            n += 3
         else:
             rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
                                          rd.ptr(rec_mine), 0, slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, 1,
@@ -417,6 +456,7 @@ def main():
         "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
         "us_per_layer": ms_dev / K / n_layers * 1e3,
     }
+    out["config"]["exchange"] = exchange
     if rank == 0 and world == 1:
         out["prefill"] = prefill_leg(rd, torch, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -138,6 +138,83 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
                       int k_type, int v_type, int n_splits, float *gate, void *workspace,
                       size_t workspace_bytes, void *stream);
 
+/* ---- many sequences in one launch (decode and short verify blocks).
+ *
+ * The reference serves one sequence per Graph (graph.cuh:958-977 decode,
+ * :1479-1535 verify); a host that batches requests calls those once per sequence. This
+ * entry takes the per-sequence caches as a host array of descriptors and runs ONE
+ * decode launch plus ONE merge for all of them: the key ranges of all sequences are cut
+ * into chunks of equal length, so ragged contexts load the SMs evenly.
+ *
+ * Sequence i has q_len new tokens; its LAST token attends keys 0..t of its cache and
+ * token j keys 0..t-(q_len-1-j) (causal inside the block, as attn_batch_kernel with
+ * pos[j] = t-(q_len-1-j)). t >= q_len-1. q / out / gate are [q_len][n_head][head_dim]
+ * f32 on the device (q 16-byte aligned); gate may be NULL, else out *= sigmoid(gate)
+ * and the sigmoid is stored back.
+ *
+ * The descriptor array is read on the host during the call; the workspace
+ * (rd_attn_multi_workspace_bytes, 256-byte aligned, device memory) receives the device
+ * copies, the work list and the partial records, and must stay untouched until the
+ * stream has passed the call. The call enqueues a host-to-device copy from pageable
+ * memory, so it cannot be part of a stream capture. */
+typedef struct rd_attn_seq {
+  const float *q;
+  const void *k;
+  const void *v;
+  float *out;
+  float *gate;
+  int32_t t;
+  int32_t reserved;
+} rd_attn_seq;
+size_t rd_attn_multi_workspace_bytes(int n_seq, int q_len, int n_head, int head_dim);
+int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
+                         int head_dim, float scale, int k_type, int v_type, void *workspace,
+                         size_t workspace_bytes, void *stream);
+
+/* ---- context-sharded decode over several GPUs, exchange fused into the merge.
+ * (No counterpart in the reference, which is single-GPU.)
+ *
+ * One process per GPU; rank r holds a contiguous slice of every layer's keys. Each rank
+ * calls this with ITS slice (k, v = start of the slice, t = index of the slice's last
+ * row, -1 for an empty slice) and the same q; every rank receives the full attention
+ * output. Instead of a library all-gather between two merges, each rank's kernel
+ * stores its per-head record (m, l, acc) directly into every rank's exchange buffer
+ * over NVLink and raises a flag there; the final merge waits for the flags.
+ *
+ *   group->xbuf[r]   rank r's exchange buffer AS MAPPED INTO THIS PROCESS (peer-mapped
+ *                    or symmetric memory; xbuf[rank] is the local one), each
+ *                    rd_shard_xbuf_bytes(...) bytes, 256-byte aligned. Zero all of them
+ *                    once and synchronise the ranks before the first call; all ranks
+ *                    must then make the same sequence of calls on the group.
+ *   wait_limit_us    how long the merge waits for the other ranks (0: one second).
+ *                    When it runs out the kernel stores zeros, records the event
+ *                    (rd_device_status returns RD_ERR_DEVICE) and returns normally.
+ *   workspace        rd_attn_workspace_bytes(1, ...), 256-byte aligned.
+ * The call is three launches on `stream` and nothing else (no copy, no allocation
+ * after the first call on a device), and keeps its call counter in the exchange
+ * buffer, so it can be captured into a CUDA graph and replayed. world <= 8.
+ *
+ * rd_attn_shard_push / rd_attn_shard_merge are the two halves of the exchange for a
+ * caller that computes the split records itself (rd_attn_decode_split with out == NULL,
+ * partial [n_head][n_splits][2 + head_dim]) or wants other work between the halves.
+ * On every rank each push must be followed by exactly one merge before the next push. */
+typedef struct rd_shard_group {
+  int32_t rank;
+  int32_t world;
+  void *const *xbuf;
+  uint32_t wait_limit_us;
+  uint32_t reserved;
+} rd_shard_group;
+size_t rd_shard_xbuf_bytes(int n_head, int head_dim, int world);
+int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *out, int t,
+                           int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                           int v_type, float *gate, void *workspace, size_t workspace_bytes,
+                           const rd_shard_group *group, void *stream);
+int rd_attn_shard_push(const float *partial, int n_splits, int n_head, int head_dim,
+                       const rd_shard_group *group, void *stream);
+int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,
+                        const rd_shard_group *group, void *stream);
+
 /* ---- single-token attention that allocates nothing. (No counterpart in the reference.)
  *
  * Some hosts cannot let a library call cudaMalloc: a serving process whose memory

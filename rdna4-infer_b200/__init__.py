@@ -45,6 +45,13 @@ SIGNATURES = {
     "rd_attn_decode_split": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P]),
     "rd_attn_decode_ws": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                C.c_size_t, _P]),
+    "rd_attn_multi_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I]),
+    "rd_attn_decode_multi": (_I, [_P, _I, _I, _I, _I, _I, _F, _I, _I, _P, C.c_size_t, _P]),
+    "rd_shard_xbuf_bytes": (C.c_size_t, [_I, _I, _I]),
+    "rd_attn_decode_sharded": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, C.c_size_t,
+                                    _P, _P]),
+    "rd_attn_shard_push": (_I, [_P, _I, _I, _I, _P, _P]),
+    "rd_attn_shard_merge": (_I, [_P, _P, _I, _I, _P, _P]),
     "rd_attn_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
     "rd_attn_merge": (_I, [_P, _P, _I, _I, _I, _P, _P]),
     "rd_attn_batch": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P]),
@@ -63,6 +70,28 @@ def build(verbose: bool = False) -> str:
         cmd.insert(1, "-s")
     subprocess.check_call(cmd)
     return LIB_PATH
+
+
+class AttnSeq(C.Structure):
+    """`rd_attn_seq` of include/rd_attn.h: one sequence of rd_attn_decode_multi."""
+
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+                ("gate", C.c_void_p), ("t", C.c_int32), ("reserved", C.c_int32)]
+
+
+class ShardGroup(C.Structure):
+    """`rd_shard_group` of include/rd_attn.h."""
+
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("xbuf", C.POINTER(C.c_void_p)),
+                ("wait_limit_us", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+def shard_group(rank, xbuf_ptrs, wait_limit_us=0):
+    """Build a ShardGroup (keeps the pointer array alive as an attribute)."""
+    arr = (C.c_void_p * len(xbuf_ptrs))(*[int(p) for p in xbuf_ptrs])
+    g = ShardGroup(rank, len(xbuf_ptrs), C.cast(arr, C.POINTER(C.c_void_p)), wait_limit_us, 0)
+    g._keepalive = arr
+    return g
 
 
 class RdError(RuntimeError):

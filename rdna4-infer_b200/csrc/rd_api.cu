@@ -1,5 +1,7 @@
 // extern "C" entry points: argument validation, split planning, per-device workspace.
+#include <algorithm>
 #include <mutex>
+#include <vector>
 #include <string.h>
 
 #include "rd_common.cuh"
@@ -385,6 +387,201 @@ int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *
   return attn_core(q, k, v, out, nullptr, 1, nullptr, t, 0, 1, n_head, n_head_kv, scale, k_type,
                    v_type, gate, records, kNoAllocFloats * sizeof(float), status_word(dev, false),
                    sms, (cudaStream_t)stream);
+}
+
+// ---- multi-sequence decode / verify -------------------------------------------------
+// Workspace layout: [n_seq descriptors][work items][records]; every part 256-aligned.
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static int multi_max_items(int sms, int n_seq, int q_len) { return 4 * sms + n_seq * q_len; }
+
+size_t rd_attn_multi_workspace_bytes(int n_seq, int q_len, int n_head, int head_dim) {
+  int dev;
+  if (n_seq < 1 || q_len < 1 || n_head < 1 || head_dim != kHeadDim ||
+      current_device(&dev) != RD_OK)
+    return 0;
+  const size_t items = (size_t)multi_max_items(sm_count(dev), n_seq, q_len);
+  return align256((size_t)n_seq * sizeof(DecodeSeq)) + align256(items * sizeof(int4)) +
+         align256(items * (size_t)n_head * kRec * sizeof(float));
+}
+
+int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
+                         int head_dim, float scale, int k_type, int v_type, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (n_seq < 0 || q_len < 1) return RD_ERR_SHAPE;
+  if (n_seq == 0) return RD_OK;
+  if (seqs == nullptr) return RD_ERR_NULL;
+  if (workspace == nullptr) return RD_ERR_WORKSPACE;
+  if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
+  for (int i = 0; i < n_seq; ++i) {
+    const rd_attn_seq &s = seqs[i];
+    if (s.q == nullptr || s.k == nullptr || s.v == nullptr || s.out == nullptr) return RD_ERR_NULL;
+    if (!aligned(s.q, 16) || !aligned(s.out, 4) || !aligned(s.gate, 4)) return RD_ERR_ALIGN;
+    if (!aligned(s.k, 16) || !aligned(s.v, 16)) return RD_ERR_ALIGN;
+    if (s.t < q_len - 1) return RD_ERR_SHAPE;  // every new token needs at least its own key
+  }
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  const int sms = sm_count(dev);
+  const int max_items = multi_max_items(sms, n_seq, q_len);
+  const size_t off_items = align256((size_t)n_seq * sizeof(DecodeSeq));
+  const size_t off_rec = off_items + align256((size_t)max_items * sizeof(int4));
+  const size_t need = off_rec + align256((size_t)max_items * n_head * kRec * sizeof(float));
+  if (workspace_bytes < need) return RD_ERR_WORKSPACE;
+
+  // Key split: chunks of equal length over all sequences, about four CTAs per SM in
+  // total, so that a 32k-key sequence and a 1k-key one load the SMs evenly.
+  const int tile = decode_tile_keys(k_type, v_type);
+  std::vector<int> tiles(n_seq);
+  int64_t total = 0;
+  for (int i = 0; i < n_seq; ++i) {
+    tiles[i] = (seqs[i].t + tile) / tile;  // ceil((t + 1) / tile)
+    total += (int64_t)tiles[i] * q_len;
+  }
+  int64_t chunk = (total + 4 * sms - 1) / (4 * sms);
+  if (chunk < 4) chunk = 4;
+  std::vector<unsigned char> host(off_rec);
+  DecodeSeq *hs = reinterpret_cast<DecodeSeq *>(host.data());
+  int4 *hi = reinterpret_cast<int4 *>(host.data() + off_items);
+  std::vector<int> order(n_seq);
+  for (int i = 0; i < n_seq; ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tiles[a] > tiles[b]; });
+  int64_t rec_base = 0;
+  int n_items = 0;
+  for (int i = 0; i < n_seq; ++i) {
+    DecodeSeq &d = hs[i];
+    memset(&d, 0, sizeof(d));
+    d.q = seqs[i].q;
+    d.k = (const uint8_t *)seqs[i].k;
+    d.v = (const uint8_t *)seqs[i].v;
+    d.out = seqs[i].out;
+    d.gate = seqs[i].gate;
+    d.t = seqs[i].t;
+    int ns = (int)((tiles[i] + chunk - 1) / chunk);
+    d.n_splits = ns < 1 ? 1 : ns;
+    d.rec_base = (int)rec_base;
+    rec_base += (int64_t)d.n_splits * q_len * n_head;
+  }
+  for (int oi = 0; oi < n_seq; ++oi) {  // longest sequences first
+    const int i = order[oi];
+    for (int sp = 0; sp < hs[i].n_splits; ++sp)
+      for (int tok = 0; tok < q_len; ++tok) {
+        if (n_items >= max_items) return RD_ERR_WORKSPACE;  // cannot happen by the bound above
+        hi[n_items++] = make_int4(i, tok, sp, 0);
+      }
+  }
+  MultiDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.host_seqs = hs;
+  a.n_seq = n_seq;
+  a.n_head_kv = n_head_kv;
+  if ((rc = launch_decode_multi(k_type, v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
+  // The host vector is pageable: the copy has left it when cudaMemcpyAsync returns.
+  if (cudaMemcpyAsync(workspace, host.data(), off_items + (size_t)n_items * sizeof(int4),
+                      cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess)
+    return RD_ERR_CUDA;
+  a.host_seqs = nullptr;
+  a.dev_seqs = reinterpret_cast<const DecodeSeq *>(workspace);
+  a.dev_items = reinterpret_cast<const int4 *>((const unsigned char *)workspace + off_items);
+  a.n_items = n_items;
+  a.q_len = q_len;
+  a.n_head = n_head;
+  a.scale = scale;
+  a.records = reinterpret_cast<float *>((unsigned char *)workspace + off_rec);
+  a.status = status_word(dev, false);
+  if ((rc = launch_decode_multi(k_type, v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
+  return launch_merge_multi(a.dev_seqs, a.records, n_seq, q_len, n_head, (cudaStream_t)stream);
+}
+
+// ---- context-sharded decode with the exchange fused into the merge -------------------
+size_t rd_shard_xbuf_bytes(int n_head, int head_dim, int world) {
+  if (n_head < 1 || head_dim != kHeadDim || world < 1 || world > kShardMaxWorld) return 0;
+  return align256(kShardHeaderBytes + (size_t)2 * world * n_head * kRec * sizeof(float));
+}
+
+// Validates a group and converts it; RD_OK or an error.
+static int shard_peers(const rd_shard_group *group, ShardPeers *g) {
+  if (group == nullptr || group->xbuf == nullptr) return RD_ERR_NULL;
+  if (group->world < 1 || group->world > kShardMaxWorld || group->rank < 0 ||
+      group->rank >= group->world)
+    return RD_ERR_SHAPE;
+  memset(g, 0, sizeof(*g));
+  for (int r = 0; r < group->world; ++r) {
+    if (group->xbuf[r] == nullptr) return RD_ERR_NULL;
+    if (!aligned(group->xbuf[r], 256)) return RD_ERR_ALIGN;
+    g->x[r] = (unsigned char *)group->xbuf[r];
+  }
+  g->rank = group->rank;
+  g->world = group->world;
+  g->wait_ns = 1000ull * (group->wait_limit_us != 0 ? group->wait_limit_us : 1000000u);
+  return RD_OK;
+}
+
+int rd_attn_shard_push(const float *partial, int n_splits, int n_head, int head_dim,
+                       const rd_shard_group *group, void *stream) {
+  if (n_head < 1 || n_splits < 1) return RD_ERR_SHAPE;
+  if (head_dim != kHeadDim) return RD_ERR_UNSUPPORTED;
+  if (partial == nullptr) return RD_ERR_NULL;
+  if (!aligned(partial, 4)) return RD_ERR_ALIGN;
+  ShardPeers g;
+  const int rc = shard_peers(group, &g);
+  if (rc != RD_OK) return rc;
+  return launch_shard_push(partial, n_splits, n_head, g, (cudaStream_t)stream);
+}
+
+int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,
+                        const rd_shard_group *group, void *stream) {
+  if (n_head < 1) return RD_ERR_SHAPE;
+  if (head_dim != kHeadDim) return RD_ERR_UNSUPPORTED;
+  if (out == nullptr) return RD_ERR_NULL;
+  if (!aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
+  ShardPeers g;
+  int rc = shard_peers(group, &g);
+  if (rc != RD_OK) return rc;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  return launch_shard_merge(out, gate, n_head, g, status_word(dev, true), (cudaStream_t)stream);
+}
+
+int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *out, int t,
+                           int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                           int v_type, float *gate, void *workspace, size_t workspace_bytes,
+                           const rd_shard_group *group, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return RD_ERR_NULL;
+  if (t < -1) return RD_ERR_SHAPE;
+  ShardPeers g;
+  if ((rc = shard_peers(group, &g)) != RD_OK) return rc;
+  if (workspace == nullptr) return RD_ERR_WORKSPACE;
+  if (!aligned(q, 4) || !aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
+  if (!aligned(k, 16) || !aligned(v, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  const int tile = decode_tile_keys(k_type, v_type);
+  const int64_t tiles = ((int64_t)t + tile) / tile;  // ceil((t + 1) / tile); 0 for an empty slice
+  const int S = plan_splits(sm_count(dev), 1, tiles);
+  if (workspace_bytes < partial_floats(1, n_head, S) * sizeof(float)) return RD_ERR_WORKSPACE;
+  DeviceStatus *status = status_word(dev, true);
+  DecodeArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.partial = (float *)workspace;
+  a.pos = nullptr;
+  a.t = t;
+  a.key_begin = 0;
+  a.n_tok = 1;
+  a.n_head = n_head;
+  a.n_head_kv = n_head_kv;
+  a.scale = scale;
+  a.n_splits = S;
+  a.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = launch_decode(k_type, v_type, a, st)) != RD_OK) return rc;
+  if ((rc = launch_shard_push((const float *)workspace, S, n_head, g, st)) != RD_OK) return rc;
+  return launch_shard_merge(out, gate, n_head, g, status, st);
 }
 
 int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,

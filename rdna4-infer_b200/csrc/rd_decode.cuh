@@ -373,9 +373,14 @@ struct DecodeKernelArgs {
   int debug;  // 0 normal; timing experiments only, bit mask: 1 consumers skip all math, 2 producer
               // skips the copies, 4 skip QK, 8 skip PV, 16 skip the softmax
   DeviceStatus *status;
+  // Multi-sequence launches (MULTI): one CTA per work item (sequence, token, split);
+  // everything per-sequence comes from the descriptor instead of the fields above.
+  const DecodeSeq *seqs;
+  const int4 *items;
+  int q_len;
 };
 
-template <int KT, int VT>
+template <int KT, int VT, bool MULTI>
 __global__ void __launch_bounds__((4 * key_groups(KT, VT) + 1) * 32, 1)
 decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   constexpr int KG = key_groups(KT, VT);
@@ -404,15 +409,51 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   float *qstage = reinterpret_cast<float *>(smem + 16 * kMaxStages);
   const uint32_t tiles0 = bar_full + kRingOffset;            // 128-byte aligned
 
-  const int qt = blockIdx.y;
-  const int t_last = p.pos != nullptr ? p.pos[qt] : p.t;
-  const int n_keys = t_last >= p.key_begin ? t_last - p.key_begin + 1 : 0;
+  // What this CTA works on: token qt, split s of S, keys key_begin..t_last of the caches
+  // at kbase / vbase (or behind the tensor maps tmk / tmv), one record per head at
+  // rec0 + head * S * kRec.
+  int qt, s, S, t_last, key_begin, use_tk, use_tv;
+  const float *qsrc;
+  const uint8_t *kbase, *vbase;
+  const CUtensorMap *tmk, *tmv;
+  float *rec0;
+  if constexpr (MULTI) {
+    const int4 item = p.items[blockIdx.x];
+    const DecodeSeq &d = p.seqs[item.x];
+    qt = item.y;
+    s = item.z;
+    S = d.n_splits;
+    t_last = d.t - (p.q_len - 1 - qt);  // causal inside the block of q_len new tokens
+    key_begin = 0;
+    use_tk = d.k_tmap;
+    use_tv = d.v_tmap;
+    qsrc = d.q + (size_t)qt * p.n_head * kHeadDim;
+    kbase = d.k;
+    vbase = d.v;
+    tmk = reinterpret_cast<const CUtensorMap *>(d.tm_k);
+    tmv = reinterpret_cast<const CUtensorMap *>(d.tm_v);
+    rec0 = p.partial + ((size_t)d.rec_base + (size_t)qt * p.n_head * S + s) * kRec;
+  } else {
+    qt = blockIdx.y;
+    s = blockIdx.x;
+    S = gridDim.x;
+    t_last = p.pos != nullptr ? p.pos[qt] : p.t;
+    key_begin = p.key_begin;
+    use_tk = p.k_tmap;
+    use_tv = p.v_tmap;
+    qsrc = p.q + (size_t)qt * p.n_head * kHeadDim;
+    kbase = p.k;
+    vbase = p.v;
+    tmk = &p.tm_k;
+    tmv = &p.tm_v;
+    rec0 = p.partial + ((size_t)qt * p.n_head * S + s) * kRec;
+  }
+  const int n_keys = t_last >= key_begin ? t_last - key_begin + 1 : 0;
   const int tiles_total = (n_keys + TILE - 1) / TILE;
-  const int S = gridDim.x, s = blockIdx.x;
   const int tile_b = (int)(((int64_t)tiles_total * s) / S);
   const int tile_e = (int)(((int64_t)tiles_total * (s + 1)) / S);
   const int ntiles = tile_e - tile_b;
-  const int key0 = p.key_begin + tile_b * TILE;
+  const int key0 = key_begin + tile_b * TILE;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -427,7 +468,7 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     // Query rows of this token -> shared memory, pre-scaled into log2 units (and by the
     // loader's fixed-point factor), coalesced; the producer warp is already streaming.
     const float qmul = p.qscale * KL::kUnscale;
-    const float4 *q4 = reinterpret_cast<const float4 *>(p.q + (size_t)qt * p.n_head * kHeadDim);
+    const float4 *q4 = reinterpret_cast<const float4 *>(qsrc);
     for (int i = threadIdx.x; i < nkv * kGroup * (kHeadDim / 4); i += CW * 32) {
       const int head = i >> 6, c4 = i & 63;
       const float4 v = q4[i];
@@ -475,22 +516,22 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
         continue;
       }
       if (lane == 0)
-        mbar_expect_tx(full, TILE * ((p.k_tmap ? pitch_k : kb) + (p.v_tmap ? pitch_v : vb)));
+        mbar_expect_tx(full, TILE * ((use_tk ? pitch_k : kb) + (use_tv ? pitch_v : vb)));
       __syncwarp();
       const uint32_t sk = tiles0 + st * stage_bytes;
       const uint32_t sv = sk + v_tile_off;
       const int row0 = key0 + it * TILE;
-      if (p.k_tmap) {
-        if (lane == 0) tma_load_2d(sk, &p.tm_k, 0, row0, full);
+      if (use_tk) {
+        if (lane == 0) tma_load_2d(sk, tmk, 0, row0, full);
       } else if (lane < TILE) {
         const int key = row0 + lane > t_last ? t_last : row0 + lane;  // tail rows repeat the last key
-        bulk_g2s(sk + lane * pitch_k, p.k + (size_t)key * kb, kb, full);
+        bulk_g2s(sk + lane * pitch_k, kbase + (size_t)key * kb, kb, full);
       }
-      if (p.v_tmap) {
-        if (lane == 0) tma_load_2d(sv, &p.tm_v, 0, row0, full);
+      if (use_tv) {
+        if (lane == 0) tma_load_2d(sv, tmv, 0, row0, full);
       } else if (lane < TILE) {
         const int key = row0 + lane > t_last ? t_last : row0 + lane;
-        bulk_g2s(sv + lane * pitch_v, p.v + (size_t)key * vb, vb, full);
+        bulk_g2s(sv + lane * pitch_v, vbase + (size_t)key * vb, vb, full);
       }
     }
   } else if (active) {
@@ -722,7 +763,7 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
       s_wgt[w][h] = wgt;
       ll += rec[1] * wgt;
     }
-    float *out = p.partial + (((size_t)qt * p.n_head + h) * S + s) * kRec;
+    float *out = rec0 + (size_t)h * S * kRec;
     out[0] = (mm == -INFINITY || s_abort) ? -INFINITY : mm * 0.6931471805599453f;  // natural log
     out[1] = ll;
   }
@@ -734,16 +775,16 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     float acc = 0.f;
 #pragma unroll
     for (int w = 0; w < KG; ++w) acc += stg[(w * nkv + hk) * kStgWarp + off] * s_wgt[w][h];
-    p.partial[(((size_t)qt * p.n_head + h) * S + s) * kRec + 2 + d] = acc;
+    rec0[(size_t)h * S * kRec + 2 + d] = acc;
   }
 }
 
-// Host side of one (KT, VT) instantiation.
-template <int KT, int VT>
-int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
+// Shared-memory plan of one (KT, VT) instantiation and the opt-in for it.
+template <int KT, int VT, bool MULTI>
+int prepare_decode(int n_head_kv, int *stages_out, size_t *smem_out) {
   constexpr int KG = key_groups(KT, VT);
   constexpr int TILE = 16 * KG;
-  const int pitch = key_pitch(KT, a.n_head_kv) + key_pitch(VT, a.n_head_kv);
+  const int pitch = key_pitch(KT, n_head_kv) + key_pitch(VT, n_head_kv);
   const int stage_bytes = TILE * pitch;
   int stages = (kSmemBudget - kRingOffset) / stage_bytes;
   if (stages < 1) return RD_ERR_UNSUPPORTED;
@@ -754,16 +795,32 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;
-  if (dev < 8 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(decode_kernel<KT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (dev < 0 || dev >= 8 || !attr_set[dev]) {
+    if (cudaFuncSetAttribute(decode_kernel<KT, VT, MULTI>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBudget) != cudaSuccess)
       return RD_ERR_CUDA;
-    attr_set[dev] = true;
-  } else if (dev >= 8) {
-    if (cudaFuncSetAttribute(decode_kernel<KT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBudget) != cudaSuccess)
-      return RD_ERR_CUDA;
+    if (dev >= 0 && dev < 8) attr_set[dev] = true;
   }
+  *stages_out = stages;
+  *smem_out = smem;
+  return RD_OK;
+}
+
+inline int decode_debug_mask() {
+  const char *e = getenv("RD_DECODE_DEBUG");
+  return e ? atoi(e) : 0;
+}
+
+// Host side of one (KT, VT) instantiation.
+template <int KT, int VT>
+int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
+  constexpr int KG = key_groups(KT, VT);
+  constexpr int TILE = 16 * KG;
+  int stages = 0;
+  size_t smem = 0;
+  const int rc = prepare_decode<KT, VT, false>(a.n_head_kv, &stages, &smem);
+  if (rc != RD_OK) return rc;
   DecodeKernelArgs k;
   memset(&k, 0, sizeof(k));
   // Quantized keys are small (576 / 1088 bytes for 4 kv heads), so a whole tile comes in
@@ -787,13 +844,47 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.nkv = a.n_head_kv;
   k.qscale = a.scale * 1.4426950408889634f;
   k.stages = stages;
-  {
-    const char *e = getenv("RD_DECODE_DEBUG");
-    k.debug = e ? atoi(e) : 0;
-  }
+  k.debug = decode_debug_mask();
   k.status = a.status;
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
-  decode_kernel<KT, VT><<<grid, (4 * KG + 1) * 32, smem, st>>>(k);
+  decode_kernel<KT, VT, false><<<grid, (4 * KG + 1) * 32, smem, st>>>(k);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+// Multi-sequence flavour: fills the tensor maps of the host-side descriptors (prepare)
+// and launches one CTA per work item (launch).
+template <int KT, int VT>
+int multi_decode_typed(const MultiDecodeArgs &a, cudaStream_t st) {
+  constexpr int KG = key_groups(KT, VT);
+  constexpr int TILE = 16 * KG;
+  if (a.host_seqs != nullptr) {
+    for (int i = 0; i < a.n_seq; ++i) {
+      DecodeSeq &d = a.host_seqs[i];
+      const int64_t n_rows = (int64_t)d.t + 1;
+      d.k_tmap = n_rows > 0 && KT >= RD_KV_Q8_0 &&
+                 encode_kv_tmap(d.tm_k, d.k, KT, a.n_head_kv, n_rows, TILE) == RD_OK;
+      d.v_tmap = n_rows > 0 && VT >= RD_KV_Q8_0 &&
+                 encode_kv_tmap(d.tm_v, d.v, VT, a.n_head_kv, n_rows, TILE) == RD_OK;
+    }
+    return RD_OK;
+  }
+  int stages = 0;
+  size_t smem = 0;
+  const int rc = prepare_decode<KT, VT, true>(a.n_head_kv, &stages, &smem);
+  if (rc != RD_OK) return rc;
+  DecodeKernelArgs k;
+  memset(&k, 0, sizeof(k));
+  k.partial = a.records;
+  k.n_head = a.n_head;
+  k.nkv = a.n_head_kv;
+  k.qscale = a.scale * 1.4426950408889634f;
+  k.stages = stages;
+  k.debug = decode_debug_mask();
+  k.status = a.status;
+  k.seqs = a.dev_seqs;
+  k.items = a.dev_items;
+  k.q_len = a.q_len;
+  decode_kernel<KT, VT, true><<<(unsigned)a.n_items, (4 * KG + 1) * 32, smem, st>>>(k);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 

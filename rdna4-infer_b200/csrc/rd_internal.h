@@ -40,6 +40,44 @@ struct DecodeArgs {
   DeviceStatus *status;
 };
 int launch_decode(int kt, int vt, const DecodeArgs &a, cudaStream_t st);
+
+// One sequence of a multi-sequence launch, as the kernels read it from device memory.
+// The last of the q_len new tokens attends keys 0..t, token i keys 0..t-(q_len-1-i).
+// Its records live at records[rec_base ...] as [q_len][n_head][n_splits][258].
+struct alignas(64) DecodeSeq {
+  alignas(64) unsigned char tm_k[128];  // CUtensorMap over the K cache, if k_tmap
+  alignas(64) unsigned char tm_v[128];
+  const float *q;    // [q_len][n_head][256]
+  const uint8_t *k;
+  const uint8_t *v;
+  float *out;        // [q_len][n_head][256]
+  float *gate;       // optional, like out
+  int t;
+  int n_splits;
+  int rec_base;      // in records
+  int k_tmap;
+  int v_tmap;
+  int pad_;
+};
+static_assert(sizeof(DecodeSeq) == 320, "DecodeSeq layout");
+
+// launch_decode_multi runs in two phases: with host_seqs set it only encodes the
+// tensor maps into the host-side descriptors (k_tmap / v_tmap say which exist); with
+// host_seqs null it launches n_items CTAs over the device copies.
+struct MultiDecodeArgs {
+  DecodeSeq *host_seqs;
+  int n_seq;
+  const DecodeSeq *dev_seqs;
+  const int4 *dev_items;  // (sequence, token, split, 0)
+  int n_items;
+  int q_len;
+  int n_head;
+  int n_head_kv;
+  float scale;
+  float *records;
+  DeviceStatus *status;
+};
+int launch_decode_multi(int kt, int vt, const MultiDecodeArgs &a, cudaStream_t st);
 // Keys per tile of the (kt, vt) kernel: the granularity of the key split.
 int decode_tile_keys(int kt, int vt);
 
@@ -73,5 +111,30 @@ int launch_merge(const float *partial, float *out, int n_rows, int n_splits, flo
 // input records [j*n_in/n_out, (j+1)*n_in/n_out).
 int launch_merge_records(const float *partial, float *records, int n_rows, int n_in, int n_out,
                          cudaStream_t st);
+// Multi-sequence merge: row (sequence, token, head) reads its n_splits records from the
+// sequence's block of `records` and writes (optionally gated) into the sequence's out.
+int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_seq, int q_len,
+                       int n_head, cudaStream_t st);
+
+// ---- rd_shard.cu
+// Exchange buffers of a context-sharded group, as mapped into this process: x[r] is
+// rank r's buffer (x[rank] the local one): kShardHeaderBytes of header, then
+// [2 parities][world][n_head][258] f32 records.
+constexpr int kShardMaxWorld = 8;
+constexpr size_t kShardHeaderBytes = 1024;
+struct ShardPeers {
+  unsigned char *x[kShardMaxWorld];
+  int rank;
+  int world;
+  unsigned long long wait_ns;  // how long the merge waits for the other ranks' records
+};
+// partial [n_head][n_in][258] (this rank's split records) -> one record per head stored
+// into every rank's buffer, then this call's epoch into every rank's flag.
+int launch_shard_push(const float *partial, int n_in, int n_head, const ShardPeers &g,
+                      cudaStream_t st);
+// Waits (bounded) for all ranks' records of this call, merges them into out
+// [n_head][256] (optional fused sigmoid gate) and advances the local epoch.
+int launch_shard_merge(float *out, float *gate, int n_head, const ShardPeers &g,
+                       DeviceStatus *status, cudaStream_t st);
 
 }  // namespace rd

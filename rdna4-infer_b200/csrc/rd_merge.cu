@@ -17,10 +17,12 @@ constexpr int kMergeDims = 64;    // dims per CTA
 constexpr int kMergeGroups = 16;  // record groups per CTA
 
 // MODE 0: normalised output (optionally gated). MODE 1: un-normalised record out.
+// MODE 2: like 0, but row = (sequence, token, head) and the record block, split count,
+// output and gate come from the sequence's descriptor (rows_per_seq = q_len * n_head).
 template <int MODE>
 __global__ void __launch_bounds__(kMergeDims *kMergeGroups)
 merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_in, int n_out,
-             float *__restrict__ gate) {
+             float *__restrict__ gate, const DecodeSeq *__restrict__ seqs, int rows_per_seq) {
   __shared__ float s_l[kMergeGroups];
   __shared__ float s_acc[kMergeGroups][kMergeDims];
   __shared__ float s_mm;
@@ -30,8 +32,18 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
   const int j = MODE == 1 ? blockIdx.z : 0;  // output record index
   const int tx = threadIdx.x % kMergeDims, ty = threadIdx.x / kMergeDims;
   const int lo = MODE == 1 ? (int)(((int64_t)n_in * j) / n_out) : 0;
-  const int hi = MODE == 1 ? (int)(((int64_t)n_in * (j + 1)) / n_out) : n_in;
+  int hi = MODE == 1 ? (int)(((int64_t)n_in * (j + 1)) / n_out) : n_in;
   const float *base = partial + (size_t)row * n_in * kRec;
+  int out_row = row;
+  if (MODE == 2) {
+    const DecodeSeq &d = seqs[row / rows_per_seq];
+    out_row = row % rows_per_seq;
+    n_in = d.n_splits;
+    base = partial + ((size_t)d.rec_base + (size_t)out_row * n_in) * kRec;
+    out = d.out;
+    gate = d.gate;
+    hi = n_in;
+  }
 
   // pass 1: the maximum over this output's records
   float mx = -INFINITY;
@@ -72,11 +84,11 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
       l += s_l[i];
     }
     const int d = quarter * kMergeDims + tx;
-    if (MODE == 0) {
+    if (MODE != 1) {
       float o = (mm != -INFINITY && l > 0.f) ? a / l : 0.f;
-      float *op = out + (size_t)row * kHeadDim + d;
+      float *op = out + (size_t)out_row * kHeadDim + d;
       if (gate != nullptr) {
-        float *gp = gate + (size_t)row * kHeadDim + d;
+        float *gp = gate + (size_t)out_row * kHeadDim + d;
         const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
         *gp = sg;
         o *= sg;
@@ -97,7 +109,8 @@ int launch_merge(const float *partial, float *out, int n_rows, int n_splits, flo
                  cudaStream_t st) {
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, 1);
-  merge_kernel<0><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, out, n_splits, 1, gate);
+  merge_kernel<0><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, out, n_splits, 1, gate,
+                                                              nullptr, 1);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 
@@ -106,7 +119,17 @@ int launch_merge_records(const float *partial, float *records, int n_rows, int n
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, (unsigned)n_out);
   merge_kernel<1><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, records, n_in, n_out,
-                                                               nullptr);
+                                                               nullptr, nullptr, 1);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
+int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_seq, int q_len,
+                       int n_head, cudaStream_t st) {
+  const int rows = n_seq * q_len * n_head;
+  if (rows == 0) return RD_OK;
+  const dim3 grid((unsigned)rows, kHeadDim / kMergeDims, 1);
+  merge_kernel<2><<<grid, kMergeDims * kMergeGroups, 0, st>>>(records, nullptr, 0, 1, nullptr,
+                                                              dev_seqs, q_len * n_head);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 
