@@ -235,8 +235,14 @@ def main():
         print(json.dumps({"prefill": prefill_leg(rd, torch, pk)}))
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1 and os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"    # NCCL prints its version banner to stdout otherwise
+    saved_stdout = None
+    if world > 1:
+        # NCCL prints its version banner on stdout when the first communicator comes up;
+        # the JSON line must be the only thing there, so stdout points at stderr until
+        # the line is printed.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -471,6 +477,9 @@ def main():
         out["cpu_baseline"] = {"value": bytes_layer / dt / 1e9, "unit": "GB/s", "cores": ora.num_threads(),
                                "kind": "port", "sample": "one layer-step (131001 keys) of the same workload, "
                                "CPU oracle f32 attention, OpenMP over heads", "seconds": dt}
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -61,7 +61,7 @@ enum {
   RD_ERR_CUDA = -6,        /* a CUDA runtime call or launch failed */
   RD_ERR_WORKSPACE = -7,   /* caller-provided workspace too small / workspace growth failed */
   RD_ERR_DEVICE = -8,      /* a kernel recorded a bounded-wait timeout (rd_device_status) */
-  RD_ERR_LIMIT = -9        /* a size exceeds the fixed maximum of rd_attn_decode_noalloc */
+  RD_ERR_LIMIT = -9        /* a size exceeds a fixed maximum (rd_attn_decode_noalloc, rd_attn_shard_*) */
 };
 
 const char *rd_strerror(int code);
@@ -190,7 +190,7 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
  *                    When it runs out the kernel stores zeros, records the event
  *                    (rd_device_status returns RD_ERR_DEVICE) and returns normally.
  *   workspace        rd_attn_workspace_bytes(1, ...), 256-byte aligned.
- * The call is three launches on `stream` and nothing else (no copy, no allocation
+ * The call is two launches on `stream` and nothing else (no copy, no allocation
  * after the first call on a device), and keeps its call counter in the exchange
  * buffer, so it can be captured into a CUDA graph and replayed. world <= 8.
  *

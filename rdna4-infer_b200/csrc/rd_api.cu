@@ -209,7 +209,7 @@ const char *rd_strerror(int code) {
     case RD_ERR_CUDA: return "CUDA runtime error";
     case RD_ERR_WORKSPACE: return "workspace missing or too small";
     case RD_ERR_DEVICE: return "a kernel gave up on a bounded wait";
-    case RD_ERR_LIMIT: return "size beyond the fixed maximum of the allocation-free entry point";
+    case RD_ERR_LIMIT: return "size beyond a fixed maximum of the entry point";
   }
   return "unknown error code";
 }
@@ -496,8 +496,10 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
 
 // ---- context-sharded decode with the exchange fused into the merge -------------------
 size_t rd_shard_xbuf_bytes(int n_head, int head_dim, int world) {
-  if (n_head < 1 || head_dim != kHeadDim || world < 1 || world > kShardMaxWorld) return 0;
-  return align256(kShardHeaderBytes + (size_t)2 * world * n_head * kRec * sizeof(float));
+  if (n_head < 1 || n_head > kShardMaxHeads || head_dim != kHeadDim || world < 1 ||
+      world > kShardMaxWorld)
+    return 0;
+  return align256(kShardHeaderBytes + (size_t)2 * world * n_head * 4 * kXPart * sizeof(float));
 }
 
 // Validates a group and converts it; RD_OK or an error.
@@ -522,6 +524,7 @@ int rd_attn_shard_push(const float *partial, int n_splits, int n_head, int head_
                        const rd_shard_group *group, void *stream) {
   if (n_head < 1 || n_splits < 1) return RD_ERR_SHAPE;
   if (head_dim != kHeadDim) return RD_ERR_UNSUPPORTED;
+  if (n_head > kShardMaxHeads) return RD_ERR_LIMIT;
   if (partial == nullptr) return RD_ERR_NULL;
   if (!aligned(partial, 4)) return RD_ERR_ALIGN;
   ShardPeers g;
@@ -534,6 +537,7 @@ int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,
                         const rd_shard_group *group, void *stream) {
   if (n_head < 1) return RD_ERR_SHAPE;
   if (head_dim != kHeadDim) return RD_ERR_UNSUPPORTED;
+  if (n_head > kShardMaxHeads) return RD_ERR_LIMIT;
   if (out == nullptr) return RD_ERR_NULL;
   if (!aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
   ShardPeers g;
@@ -580,8 +584,7 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
   a.status = status;
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = launch_decode(k_type, v_type, a, st)) != RD_OK) return rc;
-  if ((rc = launch_shard_push((const float *)workspace, S, n_head, g, st)) != RD_OK) return rc;
-  return launch_shard_merge(out, gate, n_head, g, status, st);
+  return launch_shard_exchange((const float *)workspace, S, out, gate, n_head, g, status, st);
 }
 
 int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,

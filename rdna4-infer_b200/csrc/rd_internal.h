@@ -119,9 +119,11 @@ int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_se
 // ---- rd_shard.cu
 // Exchange buffers of a context-sharded group, as mapped into this process: x[r] is
 // rank r's buffer (x[rank] the local one): kShardHeaderBytes of header, then
-// [2 parities][world][n_head][258] f32 records.
+// [2 parities][world][n_head][4 dim quarters][kXPart] f32 record parts.
 constexpr int kShardMaxWorld = 8;
-constexpr size_t kShardHeaderBytes = 1024;
+constexpr int kShardMaxHeads = 32;
+constexpr int kXPart = 2 + 64;  // (m, l) + one quarter of the accumulator
+constexpr size_t kShardHeaderBytes = 16384;
 struct ShardPeers {
   unsigned char *x[kShardMaxWorld];
   int rank;
@@ -136,5 +138,8 @@ int launch_shard_push(const float *partial, int n_in, int n_head, const ShardPee
 // [n_head][256] (optional fused sigmoid gate) and advances the local epoch.
 int launch_shard_merge(float *out, float *gate, int n_head, const ShardPeers &g,
                        DeviceStatus *status, cudaStream_t st);
+// Both halves in one launch.
+int launch_shard_exchange(const float *partial, int n_in, float *out, float *gate, int n_head,
+                          const ShardPeers &g, DeviceStatus *status, cudaStream_t st);
 
 }  // namespace rd

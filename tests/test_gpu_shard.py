@@ -22,7 +22,7 @@ def G(cuda):
 def make_groups(G, world, wait_limit_us=0):
     rd, lib = G.rd, G.lib
     nbytes = lib.rd_shard_xbuf_bytes(NH, HD, world)
-    assert nbytes >= 1024 + 2 * world * NH * 258 * 4
+    assert nbytes >= 2 * world * NH * 258 * 4
     bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
     groups = [rd.shard_group(r, [rd.ptr(b) for b in bufs], wait_limit_us) for r in range(world)]
     return bufs, groups
