@@ -40,7 +40,7 @@ constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
 constexpr int kPfPBytes = kPfM * kPfN * 2;                 // 16384
 // 224 KB of dynamic shared memory + < 3 KB static = the 227 KB an sm_100 CTA may use
 constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + 2 * kPfPBytes;
-constexpr int kPfThreads = 320;           // 8 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int kPfThreads = 352;           // 8 softmax warps, K TMA warp, MMA warp, V TMA warp
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemS = 0;            // columns [0, 128): two score buffers of 64
 constexpr uint32_t kTmemO = 128;          // columns [128, 384): output accumulator
@@ -144,6 +144,19 @@ __device__ __forceinline__ float rope_freq_dev(int p, int n_rot, float freq_base
 // done (long before the tile's P V), so K loads run two tiles ahead.
 enum { kBarVFull = 0, kBarVFree = 2, kBarS = 4, kBarP = 6, kBarQ = 8, kBarKFull = 9, kBarKFree = 11,
        kBarX = 13, kBarCount = 15 };
+
+// Build with -DRD_PREFILL_TRACE to accumulate clock64() spans of the per-tile phases of
+// one softmax thread and of the MMA thread of CTA (0,0) (development aid, off by default).
+#ifdef RD_PREFILL_TRACE
+__device__ unsigned long long g_pf_trace[32];
+#define RD_TR_DECL long long tr_t = clock64(); unsigned long long tr_acc[12] = {}
+#define RD_TR(i) do { const long long tr_n = clock64(); tr_acc[i] += (unsigned long long)(tr_n - tr_t); tr_t = tr_n; } while (0)
+#define RD_TR_OUT(base, n) do { if (blockIdx.x == 0 && blockIdx.y == 0) for (int tr_i = 0; tr_i < (n); ++tr_i) g_pf_trace[(base) + tr_i] = tr_acc[tr_i]; } while (0)
+#else
+#define RD_TR_DECL
+#define RD_TR(i)
+#define RD_TR_OUT(base, n)
+#endif
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -282,11 +295,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   float l_run = 0.f;                 // softmax threads: row sum
   float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
 
-  if (warp == 8) {
-    // =============================== TMA producer ==================================
-    // lane 0 feeds the K ring, lane 1 the V ring (independent waits)
-    if (lane < 2) {
-      const bool is_k = lane == 0;
+  if (warp == 8 || warp == 10) {
+    // =============================== TMA producers =================================
+    // warp 8 feeds the K ring, warp 10 the V ring. They are separate warps on purpose:
+    // two lanes of one warp waiting on different barriers hold each other up (a lane
+    // parked in try_wait parks the warp).
+    if (lane == 0) {
+      const bool is_k = warp == 8;
       const CUtensorMap *tm = is_k ? &p.tm_k : &p.tm_v;
       const int b_full = is_k ? kBarKFull : kBarVFull, b_free = is_k ? kBarKFree : kBarVFree;
       for (int j = 0; j < nt; ++j) {
@@ -315,19 +330,33 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
       // S(j) = Q K_j^T into score buffer j&1: K-major A and B, 16 steps of 16 dims,
       // 8-row groups 1 KB apart
+      // Descriptors differ only in the 16-byte-granular start address (low 14 bits, and
+      // every address here is below 256 KB), so each one is a base plus a constant.
+      const uint64_t dq = smem_desc(sQ, 16, 1024);
+      const uint64_t dk = smem_desc(sKV, 16, 1024);
+      const uint64_t dp = smem_desc(sP, 16, 1024);
+      const uint64_t dv = smem_desc(sKV + kPfKVStageBytes / 2, kPfN * 128, 1024);
+      RD_TR_DECL;
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
+        RD_TR(0);
         if (!mbar_wait(bars + 8 * (kBarKFull + st), (j >> 1) & 1, p.status, 12)) return false;
+        RD_TR(4);
         tc_fence_after();
-        const uint32_t sk = sKV + st * kPfKVStageBytes;
+        const uint64_t dks = dk + (uint64_t)((st * kPfKVStageBytes) >> 4);
+        const uint32_t d_s = tmem + kTmemS + 64 * st;
+        if (!(p.debug & 8)) {
 #pragma unroll
-        for (int kk = 0; kk < 16; ++kk) {
-          const uint64_t a = smem_desc(sQ + (kk >> 2) * (kPfM * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t b = smem_desc(sk + (kk >> 2) * (kPfN * 128) + (kk & 3) * 32, 16, 1024);
-          if (!(p.debug & 8)) tc_mma_f16(tmem + kTmemS + 64 * st, a, b, idesc_s, kk > 0);
+          for (int kk = 0; kk < 16; ++kk) {
+            const uint64_t a = dq + (uint64_t)(((kk >> 2) * (kPfM * 128) + (kk & 3) * 32) >> 4);
+            const uint64_t b = dks + (uint64_t)(((kk >> 2) * (kPfN * 128) + (kk & 3) * 32) >> 4);
+            tc_mma_f16(d_s, a, b, idesc_s, kk > 0);
+          }
         }
+        RD_TR(5);
         tc_commit(bars + 8 * (kBarS + st));
         tc_commit(bars + 8 * (kBarKFree + st));  // the K stage can be refilled
+        RD_TR(6);
         return true;
       };
       bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile written by warps 0-3
@@ -337,23 +366,29 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         const int st = j & 1;
         // next tile's scores first: the softmax warps are still busy with tile j
         if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13) ||
-            !mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
+        RD_TR(0);
+        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) { ok = false; break; }
+        RD_TR(1);
+        if (!mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
           ok = false;
           break;
         }
+        RD_TR(2);
         tc_fence_after();
         // O += P V: A = P K-major (keys), B = V MN-major: 64-dim groups 8 KB apart (LBO),
         // 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
-        const uint32_t sv = sKV + st * kPfKVStageBytes + kPfKVStageBytes / 2;
+        const uint64_t dps = dp + (uint64_t)((st * kPfPBytes) >> 4);
+        const uint64_t dvs = dv + (uint64_t)((st * kPfKVStageBytes) >> 4);
+        if (!(p.debug & 4)) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t a = smem_desc(sP + st * kPfPBytes + kk * 32, 16, 1024);
-          const uint64_t b = smem_desc(sv + kk * 2048, kPfN * 128, 1024);
-          if (!(p.debug & 4)) tc_mma_f16(tmem + kTmemO, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_f16(tmem + kTmemO, dps + (uint64_t)((kk * 32) >> 4), dvs + (uint64_t)((kk * 2048) >> 4),
+                       idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(bars + 8 * (kBarVFree + st));  // stage and P buffer reusable, O settled
+        RD_TR(3);
       }
+      RD_TR_OUT(16, 7);
       if (!ok) s_abort = 1;
     }
   } else {
@@ -361,13 +396,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
+    RD_TR_DECL;
     for (int j = 0; j < nt && ok; ++j) {
       const int st = j & 1;
       if (!mbar_wait(bars + 8 * (kBarS + st), (j >> 1) & 1, p.status, 14)) { ok = false; break; }
+      RD_TR(0);
       tc_fence_after();
       uint32_t sraw[32];
       tmem_ld32(lane_addr + kTmemS + 64 * st + 32 * ch, sraw);
       tmem_wait_ld();
+      RD_TR(1);
       const int key0 = j * kPfN + 32 * ch;
       // only tiles that reach past some row's last key need the causal mask
       if (__any_sync(0xffffffffu, key0 + 31 > my_pos)) {
@@ -380,6 +418,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[i]));
       float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       s_mx[st][ch][r] = mt;
+      RD_TR(2);
       // exchange through an mbarrier (bounded wait) rather than bar.sync: a thread that
       // gave up on a wait must not leave the others parked on a hardware barrier
       if (!(p.debug & 16)) {
@@ -388,11 +427,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       if (!mbar_wait(bars + 8 * (kBarX + st), (j >> 1) & 1, p.status, 20)) { ok = false; break; }
       }
       mt = fmaxf(mt, s_mx[st][ch ^ 1][r]);   // both halves now agree on the row maximum
+      RD_TR(3);
       // the P buffer of this parity was last read by P V of tile j-2
       if (j >= 2 && !mbar_wait(bars + 8 * (kBarVFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
         ok = false;
         break;
       }
+      RD_TR(4);
       const bool grow = mt > m_ref + kLazyThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mt);
@@ -418,6 +459,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           tmem_wait_st();
         }
       }
+      RD_TR(5);
       // P = 2^(s - m_ref) as f16: chunks 4ch..4ch+3 of row r of the K-major swizzled A tile
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       const uint32_t prow = sP + st * kPfPBytes + r * 128;
@@ -435,11 +477,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         sts128(prow + (((4 * ch + c) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      RD_TR(6);
       if (!(p.debug & 2)) fence_proxy_async();
       tc_fence_before();
+      RD_TR(7);
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarP + st));
+      RD_TR(8);
     }
+#ifdef RD_PREFILL_TRACE
+    if (threadIdx.x == 0) RD_TR_OUT(0, 9);
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) g_pf_trace[15] = (unsigned long long)nt;
+#endif
     if (ok && nt > 0 &&
         !mbar_wait(bars + 8 * (kBarVFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
       ok = false;
@@ -554,3 +603,9 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
 }
 
 }  // namespace rd
+
+#ifdef RD_PREFILL_TRACE
+extern "C" int rd_prefill_trace(unsigned long long *out32) {
+  return cudaMemcpyFromSymbol(out32, rd::g_pf_trace, sizeof(rd::g_pf_trace)) == cudaSuccess ? 0 : -6;
+}
+#endif
