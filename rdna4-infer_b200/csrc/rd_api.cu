@@ -272,6 +272,7 @@ int rd_kv_append(int k_type, int v_type, const float *k_src, const float *v_src,
   if (!known_type(k_type) || !known_type(v_type)) return RD_ERR_TYPE;
   if (n_tok < 0 || n_head_kv < 1 || head_dim < 32 || head_dim % 32 != 0) return RD_ERR_SHAPE;
   if (pos != nullptr && (n_rot < 2 || n_rot % 2 != 0 || n_rot > head_dim)) return RD_ERR_SHAPE;
+  if (pos != nullptr && n_rot > 512) return RD_ERR_UNSUPPORTED;  // frequency table of 256 pairs
   if (n_tok == 0) return RD_OK;
   if (k_src == nullptr || v_src == nullptr || k_dst == nullptr || v_dst == nullptr)
     return RD_ERR_NULL;
@@ -296,6 +297,7 @@ int rd_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float fre
             const int32_t *pos, void *stream) {
   if (n_tok < 0 || n_heads < 1 || head_dim < 2 || n_rot < 2 || n_rot % 2 != 0 || n_rot > head_dim)
     return RD_ERR_SHAPE;
+  if (n_rot > 512) return RD_ERR_UNSUPPORTED;  // frequency table of 256 pairs
   if (n_tok == 0) return RD_OK;
   if (x == nullptr || pos == nullptr) return RD_ERR_NULL;
   if (!aligned(x, 4) || !aligned(pos, 4)) return RD_ERR_ALIGN;

@@ -1,5 +1,6 @@
 // Shared device/host helpers of the sm_100a attention / KV-cache library.
 #pragma once
+#include <math.h>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -26,6 +27,24 @@ __host__ __device__ constexpr int row_bytes(int type) {
 
 // Status word written by kernels that give up on a bounded wait. Lives at the start
 // of the workspace; sticky until read by rd_device_status().
+// RoPE frequencies base^(-2p/n_rot) of the first pairs, computed on the host in double
+// and rounded once (the reference calls f32 powf, attn.cuh:39; a one-ulp difference moves
+// theta by milliradians at position 131000) and passed by value: a double pow per CTA
+// on the device costs microseconds. Pairs beyond kRopeTablePairs fall back to the
+// device computation.
+constexpr int kRopeTablePairs = 64;
+struct RopeTable {
+  float f[kRopeTablePairs];
+};
+inline RopeTable make_rope_table(int n_rot, float freq_base) {
+  RopeTable t;
+  for (int p = 0; p < kRopeTablePairs; ++p) {
+    const float e = -2.0f * (float)p / (float)n_rot;
+    t.f[p] = n_rot > 0 && p < n_rot / 2 ? (float)pow((double)freq_base, (double)e) : 0.f;
+  }
+  return t;
+}
+
 struct DeviceStatus {
   int timeout_flag;   // non-zero: some wait ran out
   int where;          // site id of the first wait that ran out

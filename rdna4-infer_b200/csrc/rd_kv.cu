@@ -106,6 +106,8 @@ __device__ __forceinline__ float rope_freq(float freq_base, int p, int n_rot) {
   const float e = -2.0f * (float)p / (float)n_rot;
   return (float)pow((double)freq_base, (double)e);
 }
+constexpr int kMaxRopePairs = 256;  // n_rot <= head_dim <= 512
+
 // sin/cos of the f32 angle with the accurate f32 routine (full-range argument
 // reduction, <= 2 ulp): what the reference's cosf/sinf do (attn.cuh:40-41), and far
 // cheaper than double for the 10^5..10^6 angles a prefill chunk needs.
@@ -120,7 +122,14 @@ __global__ void __launch_bounds__(256)
 kv_append_kernel(const float *__restrict__ ksrc, const float *__restrict__ vsrc,
                  uint8_t *__restrict__ kdst, uint8_t *__restrict__ vdst, int64_t n_blocks,
                  int head_dim, int heads_per_tok, const int32_t *__restrict__ pos, int n_rot,
-                 float freq_base) {
+                 float freq_base, const __grid_constant__ RopeTable tab) {
+  // the n_rot/2 frequencies once per CTA (a double pow per element would dominate a
+  // 512-token append)
+  __shared__ float s_freq[kMaxRopePairs];
+  if (pos != nullptr && blockIdx.y == 0 && (int)threadIdx.x < n_rot / 2)
+    s_freq[threadIdx.x] = (int)threadIdx.x < kRopeTablePairs ? tab.f[threadIdx.x]
+                                                             : rope_freq(freq_base, threadIdx.x, n_rot);
+  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int64_t blk = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (blk >= n_blocks) return;
@@ -134,7 +143,7 @@ kv_append_kernel(const float *__restrict__ ksrc, const float *__restrict__ vsrc,
         const int half = n_rot / 2;
         const int p = d < half ? d : d - half;
         const int tok = (int)(e / ((int64_t)head_dim * heads_per_tok));
-        const float theta = (float)pos[tok] * rope_freq(freq_base, p, n_rot);
+        const float theta = (float)pos[tok] * s_freq[p];
         float c, s;
         rope_cs(theta, c, s);
         const float other = ksrc[d < half ? e + half : e - half];
@@ -170,15 +179,20 @@ kv_fill_kernel(uint8_t *__restrict__ cache, int64_t n_blocks, unsigned seed) {
   store_block<T>(x, cache, blk, lane);
 }
 
-__global__ void rope_kernel(float *__restrict__ x, int n_tok, int n_heads, int head_dim, int n_rot,
-                            float freq_base, const int32_t *__restrict__ pos) {
+__global__ void __launch_bounds__(128)
+rope_kernel(float *__restrict__ x, int n_tok, int n_heads, int head_dim, int n_rot,
+            float freq_base, const int32_t *__restrict__ pos, const __grid_constant__ RopeTable tab) {
   const int pairs = n_rot / 2;
+  __shared__ float s_freq[kMaxRopePairs];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+    s_freq[i] = i < kRopeTablePairs ? tab.f[i] : rope_freq(freq_base, i, n_rot);
+  __syncthreads();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n_tok * n_heads * pairs) return;
   const int p = (int)(idx % pairs);
   const int64_t th = idx / pairs;  // token * n_heads + head
   const int tok = (int)(th / n_heads);
-  const float theta = (float)pos[tok] * rope_freq(freq_base, p, n_rot);
+  const float theta = (float)pos[tok] * s_freq[p];
   float c, s;
   rope_cs(theta, c, s);
   float *base = x + th * head_dim;
@@ -212,10 +226,11 @@ static int append_dispatch_v(int vt, const float *ks, const float *vs, uint8_t *
                              int64_t n_blocks, int head_dim, int heads_per_tok, const int32_t *pos,
                              int n_rot, float freq_base, cudaStream_t st) {
   const dim3 grid((unsigned)((n_blocks * 32 + 255) / 256), 2);
+  const RopeTable tab = make_rope_table(pos != nullptr ? n_rot : 0, freq_base);
 #define RD_V(VT)                                                                              \
   case VT:                                                                                    \
     kv_append_kernel<KT, VT><<<grid, 256, 0, st>>>(ks, vs, kd, vd, n_blocks, head_dim,        \
-                                                   heads_per_tok, pos, n_rot, freq_base);     \
+                                                   heads_per_tok, pos, n_rot, freq_base, tab); \
     break;
   switch (vt) {
     RD_V(RD_KV_F32)
@@ -278,7 +293,8 @@ int launch_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float
   const int64_t total = (int64_t)n_tok * n_heads * (n_rot / 2);
   if (total == 0) return RD_OK;
   rope_kernel<<<(unsigned)((total + 127) / 128), 128, 0, st>>>(x, n_tok, n_heads, head_dim, n_rot,
-                                                               freq_base, pos);
+                                                               freq_base, pos,
+                                                               make_rope_table(n_rot, freq_base));
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 

@@ -1,25 +1,34 @@
 // Causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
 // Replaces attn_fa2_prefill_kernel (include/rdna4/attn_fa2.cuh:30-169 of the reference)
-// for f16 K/V caches. One CTA owns a tile of 128 query tokens of ONE query head:
+// for f16 K/V caches. One CTA owns a tile of 128 query tokens of ONE query head. Tensor
+// memory (512 columns x 128 lanes, lane = query row) holds everything the tensor core
+// reads or writes except K and V:
+//   columns   0..255  O, the f32 output accumulator
+//   columns 256..383  Q as f16 pairs (the A operand of S = Q K^T, read from TMEM)
+//   columns 384..511  two score buffers of 64 f32 columns; the f16 P of a tile is
+//                     written over the first 32 columns of its buffer (the A operand of
+//                     O += P V, read from TMEM)
 //
-//   prologue   the 128 x 256 f32 query rows -> f16, scaled by scale*log2(e), optional
-//              partial RoPE, written into shared memory in the K-major 128-byte-swizzled
-//              layout tcgen05.mma reads (4 sub-tiles of [128 rows][64 dims]);
-//   per 64-key tile j (2-stage TMA ring, K and V sub-tiles of [64 keys][64 dims],
-//              hardware 128B swizzle):
-//     MMA warp   S = Q K_j^T         16 x tcgen05.mma M128 N64  K16, accumulator in TMEM
-//     8 warps    two threads per query row (= TMEM lane), 32 score columns each (row max
-//                exchanged through shared memory): tcgen05.ld the scores, causal
-//                mask (key <= pos[r]), running max with LAZY rescale (the reference point
+//   prologue   the 128 x 256 f32 query rows are loaded coalesced into a staging area,
+//              each thread takes its row: optional partial RoPE, scale*log2(e), f16,
+//              tcgen05.st into the Q columns;
+//   per 64-key tile j (K and V on separate 2-stage TMA rings, sub-tiles of
+//              [64 keys][64 dims], hardware 128B swizzle, one producer warp each):
+//     MMA warp   S = Q K_j^T         16 x tcgen05.mma M128 N64  K16 (A in TMEM, B K-major)
+//     8 warps    two threads per query row, 32 score columns each (row max exchanged
+//                through shared memory): tcgen05.ld the scores, causal mask
+//                (key <= pos[r]), running max with LAZY rescale (the reference point
 //                only moves when a row's max grows by more than 2^8, so P stays below 256
-//                in f16 and O in TMEM is rarely touched), P -> f16 into shared memory
-//     MMA warp   O += P V_j           4 x tcgen05.mma M128 N256 K16, V read MN-major
+//                in f16 and O in TMEM is rarely touched), P -> f16 pairs, tcgen05.st
+//     MMA warp   O += P V_j           4 x tcgen05.mma M128 N256 K16 (A in TMEM, B = V
+//                                     MN-major)
 //   epilogue   O / l (times sigmoid(gate) if asked) through a swizzled staging tile to
 //              coalesced f32 stores.
 //
-// Scores and P are double-buffered, so the tensor core computes S of tile j+1 while the
-// four softmax warps work on tile j, and P V of tile j while they wait for nothing else.
+// Scores are double-buffered: the tensor core computes S of tile j+1 while the softmax
+// warps work on tile j. The tensor pipe executes in issue order, which is what makes the
+// in-place P safe: S of tile j+2 is issued after P V of tile j.
 //
 // Synchronisation is mbarriers only (TMA transaction counts, tcgen05.commit); every wait
 // is bounded and a timeout unwinds the CTA (TMEM is always freed). No cluster launch, no
@@ -35,15 +44,16 @@ namespace rd {
 constexpr int kPfM = 128;                 // query rows per CTA
 constexpr int kPfN = 64;                  // keys per tile
 constexpr int kPfStages = 2;
-constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536
+constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // staging (prologue, epilogue): 65536
 constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
-constexpr int kPfPBytes = kPfM * kPfN * 2;                 // 16384
-// 224 KB of dynamic shared memory + < 3 KB static = the 227 KB an sm_100 CTA may use
-constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes + 2 * kPfPBytes;
-constexpr int kPfThreads = 352;           // 8 softmax warps, K TMA warp, MMA warp, V TMA warp
+// 192 KB of dynamic shared memory (one CTA per SM: TMEM is allocated whole)
+constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes;
+constexpr int kPfThreads = 384;           // 8 softmax warps, K TMA, S MMA, V TMA, PV MMA warps
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;            // columns [0, 128): two score buffers of 64
-constexpr uint32_t kTmemO = 128;          // columns [128, 384): output accumulator
+constexpr uint32_t kTmemO = 0;            // columns [0, 256): output accumulator
+constexpr uint32_t kTmemQ = 256;          // columns [256, 384): the query tile as f16 pairs
+constexpr uint32_t kTmemS = 384;          // columns [384, 512): two score buffers of 64; the
+                                          // f16 P of a tile overwrites its first 32 columns
 constexpr float kLazyThreshold = 8.0f;    // log2 units
 
 struct PrefillArgs {
@@ -59,6 +69,7 @@ struct PrefillArgs {
   float qscale;          // scale * log2(e)
   int n_rot;             // 0: the queries are already rotated
   float freq_base;
+  RopeTable rope;        // host-computed frequencies of the n_rot/2 <= 32 pairs
   int debug;             // timing experiments only (bit mask), 0 in production
   DeviceStatus *status;
 };
@@ -74,13 +85,15 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                           uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand lives in tensor memory (rows = lanes, two
+// f16 per 32-bit column), B behind a shared-memory descriptor.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
@@ -122,6 +135,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -131,12 +154,6 @@ __device__ __forceinline__ void tmem_wait_st() {
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
-}
-
-// RoPE frequency of pair p, correctly rounded (same arithmetic as rope_kernel, rd_kv.cu).
-__device__ __forceinline__ float rope_freq_dev(int p, int n_rot, float freq_base) {
-  const float e = -2.0f * (float)p / (float)n_rot;
-  return (float)pow((double)freq_base, (double)e);
 }
 
 // Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
@@ -182,7 +199,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   }
   const uint32_t sQ = base;
   const uint32_t sKV = sQ + kPfQBytes;                    // stage s: K at +0, V at +32 KB
-  const uint32_t sP = sKV + kPfStages * kPfKVStageBytes;
   uint8_t *gQ = smem_raw + (base - smem_u32(smem_raw));   // generic pointer to sQ
   const uint32_t bars = smem_u32(s_bars);
 
@@ -200,11 +216,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarP + i), 8);   // one elected lane per softmax warp
       mbar_init(bars + 8 * (kBarX + i), 8);
     }
-    mbar_init(bars + 8 * kBarQ, 4);          // one per prologue warp
+    mbar_init(bars + 8 * kBarQ, 8);          // one per prologue warp
     fence_barrier_init();
   }
   if (p.n_rot > 0 && (int)threadIdx.x >= 64 && (int)threadIdx.x < 64 + p.n_rot / 2)
-    s_freq[threadIdx.x - 64] = rope_freq_dev(threadIdx.x - 64, p.n_rot, p.freq_base);
+    s_freq[threadIdx.x - 64] = p.rope.f[threadIdx.x - 64];
   if (warp == 9) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -233,63 +249,72 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   const int maxpos = s_maxpos;
   const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
 
-  // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-3) ----
-  if (warp < 4) {
-    // cos/sin of every (row, pair) of this warp's 32 rows, one row per lane, parked in the
-    // (still unused) P buffers: 32 rows x up to 64 pairs... n_rot <= 64 keeps it at 8 KB
-    float2 *cs_tab = reinterpret_cast<float2 *>(smem_raw + (sP - smem_u32(smem_raw))) + warp * (32 * 32);
-    const int pairs = p.n_rot / 2;
-    if (pairs > 0) {
-      const int gr_l = row0 + warp * 32 + lane;
-      const float fpos = gr_l < p.n_q ? (float)p.pos[gr_l] : 0.f;
-      for (int i = 0; i < pairs; ++i) {
-        float c, s;
-        sincosf(fpos * s_freq[i], &s, &c);
-        cs_tab[lane * 32 + i] = make_float2(c, s);
-      }
-      __syncwarp();
-    }
+  // ---- prologue: Q rows -> f16 pairs in tensor memory (the A operand of S = Q K^T) ----
+  // Two passes of two 64-dim chunks: all 8 warps load the chunks coalesced into a staging
+  // area ([128 rows][64 floats] per chunk, 16-byte piece q of row r at q ^ (r & 15)), then
+  // warps 0-3 take the even chunk and warps 4-7 the odd one: thread = row (= TMEM lane)
+  // reads its 64 values, rotates them (chunk 0 holds all n_rot <= 64 rotated dims),
+  // scales by scale*log2(e), packs and stores 32 columns with tcgen05.st.
+  if (warp < 8) {
+    const int r = threadIdx.x & (kPfM - 1), half_id = threadIdx.x >> 7;   // row, chunk parity
+    const int gr_me = row0 + r;
+    const float fpos = gr_me < p.n_q ? (float)p.pos[gr_me] : 0.f;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      // 2 chunks x 128 rows x 16 pieces = 4096 pieces of 16 bytes, 16 per thread
 #pragma unroll 4
-    for (int rr = 0; rr < 32; ++rr) {
-      const int r = warp * 32 + rr;      // row inside the tile
-      const int gr = row0 + r;
-      float v[8];
-      if (gr < p.n_q) {
-        const float4 *src =
-            reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim) + 2 * lane;
-        const float4 a = src[0], b = src[1];
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      for (int i = 0; i < 16; ++i) {
+        const int idx = i * 256 + (int)threadIdx.x;
+        const int cpar = idx >> 11, rr = (idx >> 4) & (kPfM - 1), q = idx & 15;
+        const int gr = row0 + rr;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gr < p.n_q)
+          v = *(reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim +
+                                                 64 * (2 * pass + cpar)) + q);
+        sts128(sQ + cpar * (kPfM * 256) + rr * 256 + ((q ^ (rr & 15)) << 4), __float_as_uint(v.x),
+               __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
       }
-      if (pairs > 0) {
-        // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
-        // l and l ^ (n_rot/16) at the same element index
-        const int half_lanes = p.n_rot / 16;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      float x[64];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
-          if (lane < 2 * half_lanes) {
-            const bool lo = lane < half_lanes;
-            const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
-            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
-                      : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
+      for (int q = 0; q < 16; ++q) {
+        const float4 v = *reinterpret_cast<const float4 *>(gQ + half_id * (kPfM * 256) + r * 256 +
+                                                           ((q ^ (r & 15)) << 4));
+        x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+      }
+      if (pass == 0 && half_id == 0 && p.n_rot > 0) {
+        const int half = p.n_rot / 2;   // 8, 16, 24 or 32 pairs: (i, i + half)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i < half) {
+            float c, sn;
+            sincosf(fpos * s_freq[i], &sn, &c);
+            // the partner index is a compile-time constant only for half == 32
+            const float x0 = x[i];
+            float x1 = 0.f;
+#pragma unroll
+            for (int k = 8; k <= 32; k += 8)
+              if (half == k) x1 = x[i + k];
+            const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+            const float y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+            x[i] = y0;
+#pragma unroll
+            for (int k = 8; k <= 32; k += 8)
+              if (half == k) x[i + k] = y1;
           }
         }
       }
-      const uint32_t w0 = pack_h2(v[0] * p.qscale, v[1] * p.qscale);
-      const uint32_t w1 = pack_h2(v[2] * p.qscale, v[3] * p.qscale);
-      const uint32_t w2 = pack_h2(v[4] * p.qscale, v[5] * p.qscale);
-      const uint32_t w3 = pack_h2(v[6] * p.qscale, v[7] * p.qscale);
-      // lane = 16-byte chunk of the row: sub-tile lane/8, chunk lane%8, swizzled by the row
-      const uint32_t dst = sQ + (lane >> 3) * (kPfM * 128) + r * 128 + (((lane & 7) ^ (r & 7)) << 4);
-      sts128(dst, w0, w1, w2, w3);
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) w[i] = pack_h2(x[2 * i] * p.qscale, x[2 * i + 1] * p.qscale);
+      tmem_st32(lane_addr + kTmemQ + 32 * (2 * pass + half_id), w);
+      asm volatile("bar.sync 2, 256;" ::: "memory");   // staging free for the next pass
     }
-    fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+    tmem_wait_st();
+    tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 4 warps; TMA already runs
+    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 8 warps; TMA already runs
   }
 
   float l_run = 0.f;                 // softmax threads: row sum
@@ -324,71 +349,76 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       }
     }
   } else if (warp == 9) {
-    // =============================== MMA issuer ====================================
+    // ============================ MMA issuer: S = Q K^T =============================
+    // The two contractions are issued by two threads (this one and warp 11): issuing a
+    // tcgen05.mma costs the issuing thread tens of cycles whatever its size, and with
+    // one thread the 16 small S MMAs and the 4 P V MMAs of a tile queue up behind each
+    // other's waits.
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kPfM, kPfN, false);
-      constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
-      // S(j) = Q K_j^T into score buffer j&1: K-major A and B, 16 steps of 16 dims,
-      // 8-row groups 1 KB apart
       // Descriptors differ only in the 16-byte-granular start address (low 14 bits, and
       // every address here is below 256 KB), so each one is a base plus a constant.
-      const uint64_t dq = smem_desc(sQ, 16, 1024);
       const uint64_t dk = smem_desc(sKV, 16, 1024);
-      const uint64_t dp = smem_desc(sP, 16, 1024);
-      const uint64_t dv = smem_desc(sKV + kPfKVStageBytes / 2, kPfN * 128, 1024);
       RD_TR_DECL;
-      auto issue_s = [&](int j) -> bool {
+      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile stored by warps 0-7
+      tc_fence_after();
+      for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
         RD_TR(0);
-        if (!mbar_wait(bars + 8 * (kBarKFull + st), (j >> 1) & 1, p.status, 12)) return false;
+        if (!mbar_wait(bars + 8 * (kBarKFull + st), (j >> 1) & 1, p.status, 12)) { ok = false; break; }
         RD_TR(4);
+        // score buffer st still holds P(j-2) until P V of tile j-2 has read it
+        if (j >= 2 && !mbar_wait(bars + 8 * (kBarVFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
+          ok = false;
+          break;
+        }
+        RD_TR(1);
         tc_fence_after();
+        // S(j) into score buffer j&1: A = Q from TMEM (16 dims = 8 columns per step),
+        // B = K tile K-major, 8-row groups 1 KB apart
         const uint64_t dks = dk + (uint64_t)((st * kPfKVStageBytes) >> 4);
         const uint32_t d_s = tmem + kTmemS + 64 * st;
         if (!(p.debug & 8)) {
 #pragma unroll
           for (int kk = 0; kk < 16; ++kk) {
-            const uint64_t a = dq + (uint64_t)(((kk >> 2) * (kPfM * 128) + (kk & 3) * 32) >> 4);
             const uint64_t b = dks + (uint64_t)(((kk >> 2) * (kPfN * 128) + (kk & 3) * 32) >> 4);
-            tc_mma_f16(d_s, a, b, idesc_s, kk > 0);
+            tc_mma_f16_ts(d_s, tmem + kTmemQ + 8 * kk, b, idesc_s, kk > 0);
           }
         }
         RD_TR(5);
         tc_commit(bars + 8 * (kBarS + st));
         tc_commit(bars + 8 * (kBarKFree + st));  // the K stage can be refilled
         RD_TR(6);
-        return true;
-      };
-      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile written by warps 0-3
-      tc_fence_after();
-      ok = ok && (nt == 0 || issue_s(0));
+      }
+      RD_TR_OUT(16, 7);
+      if (!ok) s_abort = 1;
+    }
+  } else if (warp == 11) {
+    // ============================ MMA issuer: O += P V ==============================
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
+      const uint64_t dv = smem_desc(sKV + kPfKVStageBytes / 2, kPfN * 128, 1024);
+      bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
-        // next tile's scores first: the softmax warps are still busy with tile j
-        if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
-        RD_TR(0);
-        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) { ok = false; break; }
-        RD_TR(1);
-        if (!mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
+        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13) ||
+            !mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
           ok = false;
           break;
         }
-        RD_TR(2);
         tc_fence_after();
-        // O += P V: A = P K-major (keys), B = V MN-major: 64-dim groups 8 KB apart (LBO),
-        // 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
-        const uint64_t dps = dp + (uint64_t)((st * kPfPBytes) >> 4);
+        // A = P(j) from TMEM (16 keys = 8 columns per step), B = V MN-major: 64-dim groups
+        // 8 KB apart (LBO), 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
         const uint64_t dvs = dv + (uint64_t)((st * kPfKVStageBytes) >> 4);
+        const uint32_t a_p = tmem + kTmemS + 64 * st;
         if (!(p.debug & 4)) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tc_mma_f16(tmem + kTmemO, dps + (uint64_t)((kk * 32) >> 4), dvs + (uint64_t)((kk * 2048) >> 4),
-                       idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_f16_ts(tmem + kTmemO, a_p + 8 * kk, dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                          (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bars + 8 * (kBarVFree + st));  // stage and P buffer reusable, O settled
-        RD_TR(3);
+        tc_commit(bars + 8 * (kBarVFree + st));  // V stage and score buffer reusable, O settled
       }
-      RD_TR_OUT(16, 7);
       if (!ok) s_abort = 1;
     }
   } else {
@@ -421,18 +451,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       RD_TR(2);
       // exchange through an mbarrier (bounded wait) rather than bar.sync: a thread that
       // gave up on a wait must not leave the others parked on a hardware barrier
-      if (!(p.debug & 16)) {
+      // (this exchange also orders both halves' score loads before either half
+      // overwrites the buffer with P)
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarX + st));
       if (!mbar_wait(bars + 8 * (kBarX + st), (j >> 1) & 1, p.status, 20)) { ok = false; break; }
-      }
       mt = fmaxf(mt, s_mx[st][ch ^ 1][r]);   // both halves now agree on the row maximum
       RD_TR(3);
-      // the P buffer of this parity was last read by P V of tile j-2
-      if (j >= 2 && !mbar_wait(bars + 8 * (kBarVFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
-        ok = false;
-        break;
-      }
       RD_TR(4);
       const bool grow = mt > m_ref + kLazyThreshold;
       if (__any_sync(0xffffffffu, grow)) {
@@ -460,25 +485,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
       }
       RD_TR(5);
-      // P = 2^(s - m_ref) as f16: chunks 4ch..4ch+3 of row r of the K-major swizzled A tile
+      // P = 2^(s - m_ref) as f16 pairs, written over the score buffer: keys 32ch..32ch+31
+      // of row r become columns 16ch..16ch+15 (the A operand of P V, read from TMEM)
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t prow = sP + st * kPfPBytes + r * 128;
+      uint32_t pw[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {  // 8 keys = one 16-byte chunk
-        uint32_t w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int i = 8 * c + 2 * q;
-          const float p0 = (p.debug & 1) ? __uint_as_float(sraw[i]) : ex2(__uint_as_float(sraw[i]) - m_ref);
-          const float p1 = (p.debug & 1) ? __uint_as_float(sraw[i + 1]) : ex2(__uint_as_float(sraw[i + 1]) - m_ref);
-          ls[q] += p0 + p1;
-          w[q] = pack_h2(p0, p1);
-        }
-        sts128(prow + (((4 * ch + c) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = (p.debug & 1) ? __uint_as_float(sraw[2 * i]) : ex2(__uint_as_float(sraw[2 * i]) - m_ref);
+        const float p1 = (p.debug & 1) ? __uint_as_float(sraw[2 * i + 1]) : ex2(__uint_as_float(sraw[2 * i + 1]) - m_ref);
+        ls[i & 3] += p0 + p1;
+        pw[i] = pack_h2(p0, p1);
       }
+      tmem_st16(lane_addr + kTmemS + 64 * st + 16 * ch, pw);
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       RD_TR(6);
-      if (!(p.debug & 2)) fence_proxy_async();
+      tmem_wait_st();
       tc_fence_before();
       RD_TR(7);
       __syncwarp();
@@ -583,6 +604,7 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   a.qscale = scale * 1.4426950408889634f;
   a.n_rot = n_rot;
   a.freq_base = freq_base;
+  a.rope = make_rope_table(n_rot, freq_base);
   a.status = status;
   {
     const char *e = getenv("RD_PREFILL_DEBUG");
