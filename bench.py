@@ -199,6 +199,73 @@ def prefill_leg(rd, torch, peaks):
     return res
 
 
+def batched_leg(rd, torch, dist, rank, world, peak):
+    """Secondary measurement: BASELINE config 5 -- 64 sequences, context lengths uniform in
+    [1024, 32768] from seed 7, K q8_0 / V f16, q_len 1 (decode) and 4 (verify block), all
+    sequences of a rank in ONE rd_attn_decode_multi call. With N GPUs the sequences are
+    dealt out greedily by length (longest first to the least loaded rank); there is no
+    exchange. GB/s counts every K and V byte once per step, summed over ranks, over the
+    slowest rank's time."""
+    import numpy as np
+    L = rd.lib
+    lens = [int(x) for x in np.random.default_rng(7).integers(1024, 32769, size=64)]
+    load = [0] * world
+    mine = []
+    for i in sorted(range(64), key=lambda i: -lens[i]):
+        r = min(range(world), key=lambda r: load[r])
+        load[r] += lens[i]
+        if r == rank:
+            mine.append(i)
+    st = rd.stream_ptr()
+    kcs, vcs = [], []
+    for i in mine:
+        n = lens[i]
+        kc = torch.empty(n * NKV * 272, dtype=torch.uint8, device="cuda")
+        vc = torch.empty(n * NKV * 512, dtype=torch.uint8, device="cuda")
+        rd.check(L.rd_kv_fill(2, rd.ptr(kc), n * NKV, HD, 1000 + i, st))
+        rd.check(L.rd_kv_fill(1, rd.ptr(vc), n * NKV, HD, 2000 + i, st))
+        kcs.append(kc)
+        vcs.append(vc)
+    total_bytes = sum(lens) * NKV * (272 + 512)
+    res = {"unit": "GB/s", "sequences": 64, "kv_bytes_per_step": total_bytes,
+           "sharding": f"sequences dealt greedily by length over {world} GPU(s), no exchange"}
+    for q_len in (1, 4):
+        n = len(mine)
+        qs = [torch.randn(q_len, NH, HD, device="cuda") for _ in mine]
+        outs = [torch.empty(q_len, NH, HD, device="cuda") for _ in mine]
+        arr = (rd.AttnSeq * max(n, 1))()
+        for k, i in enumerate(mine):
+            arr[k].q, arr[k].k, arr[k].v = rd.ptr(qs[k]), rd.ptr(kcs[k]), rd.ptr(vcs[k])
+            arr[k].out, arr[k].t = rd.ptr(outs[k]), lens[i] - 1
+        nb = L.rd_attn_multi_workspace_bytes(max(n, 1), q_len, NH, HD)
+        ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+
+        def call():
+            rd.check(L.rd_attn_decode_multi(ctypes.addressof(arr), n, q_len, NH, NKV, HD, SCALE, 2, 1,
+                                            rd.ptr(ws), nb, rd.stream_ptr()))
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        reps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        gbs = total_bytes / (ms * 1e-3) / 1e9
+        res[f"q_len_{q_len}"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_hbm_peak_x_gpus": gbs / (peak * world),
+                                 "gpu_launches_per_step": 2}
+    return res
+
+
 def workload_config(n_gpus):
     return {"workload": "decode q_len=1, ctx 131072 (pos 131000 -> 131001 keys), 24Q/4KV heads, hd 256, "
                         "K,V q4_0, 16 layer caches per step",
@@ -465,6 +532,9 @@ def main():
     out["config"]["exchange"] = exchange
     if rank == 0 and world == 1:
         out["prefill"] = prefill_leg(rd, torch, peaks)
+    batched = batched_leg(rd, torch, dist, rank, world, peak)
+    if rank == 0:
+        out["batched_decode"] = batched
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle.oracle import Oracle
         ora = Oracle()

@@ -28,8 +28,8 @@
  * Every function returns RD_OK (0) or a negative RD_ERR_* code; nothing aborts and
  * nothing traps on the device. Shapes outside the supported set are refused with
  * RD_ERR_UNSUPPORTED: head_dim must be 256, n_head == 6 * n_head_kv, n_head_kv in
- * {1, 2, 4}; K/V types f32, f16, q8_0, q4_0 for attention (q5_0 / q4_1 are stored and
- * filled but not yet attended).
+ * {1, 2, 4}; all six K/V types in every combination for decode / batch attention
+ * (attn.cuh:203-246), f16 / f16 for the prefill tile kernel (attn_fa2.cuh:177-180).
  */
 #ifndef RD_ATTN_H
 #define RD_ATTN_H

@@ -76,7 +76,6 @@ int check_attn_shape(int n_head, int n_head_kv, int head_dim, int kt, int vt) {
   if (n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv != 0) return RD_ERR_SHAPE;
   if (head_dim != kHeadDim || n_head / n_head_kv != kGroup) return RD_ERR_UNSUPPORTED;
   if (n_head_kv != 1 && n_head_kv != 2 && n_head_kv != 4) return RD_ERR_UNSUPPORTED;
-  if (kt > RD_KV_Q4_0 || vt > RD_KV_Q4_0) return RD_ERR_UNSUPPORTED;
   return RD_OK;
 }
 

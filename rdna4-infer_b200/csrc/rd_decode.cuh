@@ -213,6 +213,63 @@ struct KLoad<RD_KV_F32> {
   }
 };
 
+// ---- q5_0 / q4_1: element-wise loaders -------------------------------------------------
+// The reference's default 131K configuration stores K as q5_0 and V as q4_1
+// (include/rdna4/kv.h:75-98). Their 22- and 20-byte blocks are read here value by value
+// (kv_load of kv.h:208-229 restated on shared memory): correct for every K x V pair, but
+// without the word-wide unpacking tricks of the q4_0 / q8_0 loaders above.
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return __half2float(__ushort_as_half(v));
+}
+template <int T>
+__device__ __forceinline__ float dequant_elem(uint32_t row, int d);
+template <>
+__device__ __forceinline__ float dequant_elem<RD_KV_Q5_0>(uint32_t row, int d) {
+  const uint32_t b = row + 22u * (uint32_t)(d >> 5);
+  const int j = d & 31;
+  const uint32_t byte = lds_u8(b + 6 + (j & 15));
+  const int nib = j < 16 ? (int)(byte & 15u) : (int)(byte >> 4);
+  const int hi = (int)(lds_u8(b + 2 + (j >> 3)) >> (j & 7)) & 1;
+  return lds_f16(b) * (float)((nib | (hi << 4)) - 16);
+}
+template <>
+__device__ __forceinline__ float dequant_elem<RD_KV_Q4_1>(uint32_t row, int d) {
+  const uint32_t b = row + 20u * (uint32_t)(d >> 5);
+  const int j = d & 31;
+  const uint32_t byte = lds_u8(b + 4 + (j & 15));
+  const int q = j < 16 ? (int)(byte & 15u) : (int)(byte >> 4);
+  return __fadd_rn(__fmul_rn(lds_f16(b), (float)q), lds_f16(b + 2));
+}
+
+template <int T>
+struct KLoadElem {
+  static constexpr float kUnscale = 1.0f;
+  // the plain m16n8k16 A layout: slots (2t, 2t+1, 2t+8, 2t+9) of k-step n
+  __device__ static int dim(int t, int n, int e) { return 16 * n + 2 * t + (e & 1) + 8 * (e >> 1); }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      const int d0 = 16 * n + 2 * t;
+      mma(n, pack_h2(dequant_elem<T>(row_g, d0), dequant_elem<T>(row_g, d0 + 1)),
+          pack_h2(dequant_elem<T>(row_h, d0), dequant_elem<T>(row_h, d0 + 1)),
+          pack_h2(dequant_elem<T>(row_g, d0 + 8), dequant_elem<T>(row_g, d0 + 9)),
+          pack_h2(dequant_elem<T>(row_h, d0 + 8), dequant_elem<T>(row_h, d0 + 9)));
+    }
+  }
+};
+template <>
+struct KLoad<RD_KV_Q5_0> : KLoadElem<RD_KV_Q5_0> {};
+template <>
+struct KLoad<RD_KV_Q4_1> : KLoadElem<RD_KV_Q4_1> {};
+
 // =============================== V loaders =======================================
 // A fragment of V^T*P for M-tile m (0..15): rows g / g+8 = two true dims chosen by
 // the loader (dim(g, m, r)), k-slots = keys (2t, 2t+1, 2t+8, 2t+9) of the group.
@@ -350,6 +407,28 @@ struct VLoad<RD_KV_F32> {
     }
   }
 };
+
+template <int T>
+struct VLoadElem {
+  static constexpr float kUnscale = 1.0f;
+  // the plain A layout of V^T: rows g / g+8 of M-tile m are dims 16m+g / 16m+g+8
+  __device__ static int dim(int g, int m, int r) { return 16 * m + g + 8 * r; }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      const int d0 = 16 * m + g, d1 = d0 + 8;
+      mma(m, pack_h2(dequant_elem<T>(rows[0], d0), dequant_elem<T>(rows[1], d0)),
+          pack_h2(dequant_elem<T>(rows[0], d1), dequant_elem<T>(rows[1], d1)),
+          pack_h2(dequant_elem<T>(rows[2], d0), dequant_elem<T>(rows[3], d0)),
+          pack_h2(dequant_elem<T>(rows[2], d1), dequant_elem<T>(rows[3], d1)));
+    }
+  }
+};
+template <>
+struct VLoad<RD_KV_Q5_0> : VLoadElem<RD_KV_Q5_0> {};
+template <>
+struct VLoad<RD_KV_Q4_1> : VLoadElem<RD_KV_Q4_1> {};
 
 // =============================== kernel ==========================================
 struct DecodeKernelArgs {
@@ -523,15 +602,19 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
       const int row0 = key0 + it * TILE;
       if (use_tk) {
         if (lane == 0) tma_load_2d(sk, tmk, 0, row0, full);
-      } else if (lane < TILE) {
-        const int key = row0 + lane > t_last ? t_last : row0 + lane;  // tail rows repeat the last key
-        bulk_g2s(sk + lane * pitch_k, kbase + (size_t)key * kb, kb, full);
+      } else {
+        for (int kk = lane; kk < TILE; kk += 32) {   // TILE is 16, 32 or 48
+          const int key = row0 + kk > t_last ? t_last : row0 + kk;  // tail rows repeat the last key
+          bulk_g2s(sk + kk * pitch_k, kbase + (size_t)key * kb, kb, full);
+        }
       }
       if (use_tv) {
         if (lane == 0) tma_load_2d(sv, tmv, 0, row0, full);
-      } else if (lane < TILE) {
-        const int key = row0 + lane > t_last ? t_last : row0 + lane;
-        bulk_g2s(sv + lane * pitch_v, vbase + (size_t)key * vb, vb, full);
+      } else {
+        for (int kk = lane; kk < TILE; kk += 32) {
+          const int key = row0 + kk > t_last ? t_last : row0 + kk;
+          bulk_g2s(sv + kk * pitch_v, vbase + (size_t)key * vb, vb, full);
+        }
       }
     }
   } else if (active) {

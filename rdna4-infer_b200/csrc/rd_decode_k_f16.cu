@@ -8,6 +8,8 @@ int launch_decode_k_f16(int vt, const DecodeArgs &a, cudaStream_t st) {
     case RD_KV_F16: return launch_decode_typed<RD_KV_F16, RD_KV_F16>(a, st);
     case RD_KV_Q8_0: return launch_decode_typed<RD_KV_F16, RD_KV_Q8_0>(a, st);
     case RD_KV_Q4_0: return launch_decode_typed<RD_KV_F16, RD_KV_Q4_0>(a, st);
+    case RD_KV_Q5_0: return launch_decode_typed<RD_KV_F16, RD_KV_Q5_0>(a, st);
+    case RD_KV_Q4_1: return launch_decode_typed<RD_KV_F16, RD_KV_Q4_1>(a, st);
     default: return RD_ERR_UNSUPPORTED;
   }
 }
@@ -17,6 +19,8 @@ int launch_decode_multi_k_f16(int vt, const MultiDecodeArgs &a, cudaStream_t st)
     case RD_KV_F16: return multi_decode_typed<RD_KV_F16, RD_KV_F16>(a, st);
     case RD_KV_Q8_0: return multi_decode_typed<RD_KV_F16, RD_KV_Q8_0>(a, st);
     case RD_KV_Q4_0: return multi_decode_typed<RD_KV_F16, RD_KV_Q4_0>(a, st);
+    case RD_KV_Q5_0: return multi_decode_typed<RD_KV_F16, RD_KV_Q5_0>(a, st);
+    case RD_KV_Q4_1: return multi_decode_typed<RD_KV_F16, RD_KV_Q4_1>(a, st);
     default: return RD_ERR_UNSUPPORTED;
   }
 }

@@ -73,7 +73,7 @@ def test_argument_validation_happens_on_the_host(rd):
     # shapes the reference accepts but this build refuses, with their own code
     assert L.rd_attn_decode(p, p, p, p, 5, 24, 4, 128, 0.0625, rd.F16, rd.F16, None) == rd.ERR_UNSUPPORTED
     assert L.rd_attn_decode(p, p, p, p, 5, 32, 4, 256, 0.0625, rd.F16, rd.F16, None) == rd.ERR_UNSUPPORTED
-    assert L.rd_attn_decode(p, p, p, p, 5, 24, 4, 256, 0.0625, rd.Q5_0, rd.F16, None) == rd.ERR_UNSUPPORTED
+    assert L.rd_attn_decode(p, p, p, p, 5, 24, 4, 256, 0.0625, 6, rd.F16, None) == rd.ERR_TYPE
     assert L.rd_attn_decode(p, p, p, p, 5, 24, 4, 100, 0.0625, rd.F16, rd.F16, None) == rd.ERR_SHAPE
     assert L.rd_attn_decode(p, p, p, p, 5, 24, 5, 256, 0.0625, rd.F16, rd.F16, None) == rd.ERR_SHAPE
     assert L.rd_attn_decode_split(p, p, p, p, p, 5, 24, 4, 256, 0.0625, rd.F16, rd.F16, 0, None) == rd.ERR_SHAPE

@@ -9,6 +9,7 @@ from tests.conftest import check_attn
 
 pytestmark = pytest.mark.gpu
 T4 = (0, 1, 2, 3)
+T6 = (0, 1, 2, 3, 4, 5)   # + q5_0, q4_1: the reference's default long-context pair
 RAGGED = [1, 2, 3, 5, 7, 8, 9, 15, 16, 17, 24, 25, 31, 33, 100, 511, 512, 513, 520, 1023, 1025,
           2048, 2050]  # the reference's ragged key counts (bench_attn_gpu.hip:1338-1339)
 
@@ -41,8 +42,8 @@ def test_decode_golden(G, golden):
     G.status_ok()
 
 
-@pytest.mark.parametrize("kt", T4, ids=[TYPE_NAMES[t] for t in T4])
-@pytest.mark.parametrize("vt", T4, ids=[TYPE_NAMES[t] for t in T4])
+@pytest.mark.parametrize("kt", T6, ids=[TYPE_NAMES[t] for t in T6])
+@pytest.mark.parametrize("vt", T6, ids=[TYPE_NAMES[t] for t in T6])
 def test_decode_all_type_pairs(G, oracle, kt, vt):
     rng = np.random.default_rng(kt * 4 + vt)
     for n in (1, 37, 300):
@@ -50,6 +51,24 @@ def test_decode_all_type_pairs(G, oracle, kt, vt):
         want = oracle.attn(q[None], kc, vc, [n - 1], nkv, 1 / 16, kt, vt)[0]
         got = G.attn_decode(q, kc, vc, n - 1, kt, vt)
         check_attn(got, want, what=f"{TYPE_NAMES[kt]}/{TYPE_NAMES[vt]} n={n}")
+    G.status_ok()
+
+
+def test_q5_0_k_q4_1_v_long_context_and_verify(G, oracle):
+    """The reference's default 131K pair (K q5_0, V q4_1): a 20 000-key decode with split
+    hints, and a 4-token verify block through the batch entry."""
+    rng = np.random.default_rng(54)
+    n = 20000
+    K = rng.standard_normal((n, 4, 256)).astype(np.float32)
+    V = (rng.standard_normal((n, 4, 256)) + 0.5).astype(np.float32)   # asymmetric: what q4_1 is for
+    kc, vc = oracle.kv_store_rows(4, K), oracle.kv_store_rows(5, V)
+    q = rng.standard_normal((4, 24, 256)).astype(np.float32)
+    want = oracle.attn(q[:1], kc, vc, [n - 1], 4, 1 / 16, 4, 5)[0]
+    check_attn(G.attn_decode(q[0], kc, vc, n - 1, 4, 5), want, what="q5_0/q4_1 20000 keys")
+    check_attn(G.attn_decode(q[0], kc, vc, n - 1, 4, 5, n_splits=7), want, what="split hint 7")
+    pos = np.arange(n - 4, n, dtype=np.int32)
+    check_attn(G.attn_batch(q, kc, vc, pos, 4, 5), oracle.attn(q, kc, vc, pos, 4, 1 / 16, 4, 5),
+               what="verify q_len=4")
     G.status_ok()
 
 
@@ -183,6 +202,23 @@ def test_batch_golden_and_verify_shapes(G, oracle, golden):
     got = G.attn_batch(q, kc, vc, pos2, 2, 1)
     assert (got[0] == 0).all()
     check_attn(got, oracle.attn(q, kc, vc, pos2, 4, 1 / 16, 2, 1), what="ragged batch")
+    G.status_ok()
+
+
+@pytest.mark.parametrize("kt,vt", [(3, 3), (2, 2), (3, 2), (4, 5), (0, 3)])
+def test_batch_entry_quantized_pairs(G, oracle, kt, vt):
+    """Key counts from a device pos[] array (one bulk copy per key instead of tensor-map
+    tiles), for the type pairs whose tiles hold 32 or 48 keys."""
+    rng = np.random.default_rng(200 + 10 * kt + vt)
+    n = 700
+    K = rng.standard_normal((n, 4, 256)).astype(np.float32)
+    V = rng.standard_normal((n, 4, 256)).astype(np.float32)
+    q = rng.standard_normal((3, 24, 256)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(kt, K), oracle.kv_store_rows(vt, V)
+    pos = np.array([46, 333, n - 1], dtype=np.int32)
+    want = oracle.attn(q, kc, vc, pos, 4, 1 / 16, kt, vt)
+    check_attn(G.attn_batch(q, kc, vc, pos, kt, vt), want, what="batch")
+    check_attn(G.attn_batch(q, kc, vc, pos, kt, vt, n_splits=5), want, what="split batch")
     G.status_ok()
 
 
