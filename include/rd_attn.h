@@ -105,6 +105,30 @@ int rd_deinterleave_q_gate(const float *yq, float *q, float *gate, int n_tok, in
                            int head_dim, void *stream);
 int rd_sigmoid_gate(float *g_io, float *y_io, int64_t n, void *stream);
 
+/* ---- RMS-norm (rms_norm_launch, nn.cuh:239-243; kernel :23-63): y = x / sqrt(mean(x^2)
+ * + eps) (* w if w != NULL) per row of n_cols; x and y may alias. The sum of squares
+ * keeps the reference kernel's order; the reciprocal square root is correctly rounded. */
+int rd_rms_norm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n_cols, float eps,
+                void *stream);
+
+/* ---- fused pre-attention stage of a full-attention layer (no single counterpart: the
+ * reference runs seven launches here, graph.cuh:915-954 -- deinterleave_q_gate_launch,
+ * two rms_norm_launch, two rope_launch, two kv_store_row_launch).
+ *   q_gate   [n_tok][n_head][2*head_dim] f32: the q projection, q then gate per head
+ *   k_src, v_src   [n_tok][n_head_kv][head_dim] f32: the k and v projections
+ *   q_norm_w, k_norm_w   [head_dim] norm weights (NULL: none); eps the RMS epsilon
+ *   q_out    [n_tok][n_head][head_dim]: normalised, rotated q (input of the attention)
+ *   gate_out [n_tok][n_head][head_dim]: the gate logits, copied
+ *   k_rows, v_rows   first cache row of the n_tok new tokens (cache + pos0 * n_head_kv *
+ *                    row_bytes): k normalised, rotated, stored as k_type; v stored as v_type
+ *   pos      device int32 [n_tok]; n_rot a multiple of 64 (0: no rotation).
+ * Results equal the seven separate calls of this library bit for bit. head_dim 256. */
+int rd_pre_attn_fused(const float *q_gate, const float *k_src, const float *v_src,
+                      const float *q_norm_w, const float *k_norm_w, float eps, float *q_out,
+                      float *gate_out, void *k_rows, void *v_rows, int k_type, int v_type,
+                      const int32_t *pos, int n_tok, int n_head, int n_head_kv, int head_dim,
+                      int n_rot, float freq_base, void *stream);
+
 /* ---- partial records: attn_partial_bytes, include/rdna4/attn.cuh:665-667.
  * A record is (m, l, acc[head_dim]) f32 in natural-log units: m = max scaled score,
  * l = sum exp(s - m), acc = sum exp(s - m) * v; an empty record is (-inf, 0, 0...). */

@@ -96,6 +96,11 @@ inline bool attn_merge_launch(const float *d_partial, float *d_out, int n_head, 
 
 // nn.cuh:414-420 and gdn.cuh:377-384, 853-862 of the reference: the gate glue around
 // the attention call (kept here so that one include serves Graph::full_attn).
+// nn.cuh:239-243 of the reference.
+inline bool rms_norm_launch(const float *d_x, const float *d_w, float *d_y, std::int64_t nrows,
+                            std::int64_t ncols, float eps, cudaStream_t stream = nullptr) {
+  return rd_rms_norm(d_x, d_w, d_y, nrows, ncols, eps, stream) == RD_OK;
+}
 inline bool sigmoid_gate_launch(float *d_g_io, float *d_y_io, std::int64_t n,
                                 cudaStream_t stream = nullptr) {
   return rd_sigmoid_gate(d_g_io, d_y_io, n, stream) == RD_OK;

@@ -76,6 +76,8 @@ class Oracle(_AttnMixin):
         L.rdo_rope.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]
         L.rdo_sigmoid_gate.restype = None
         L.rdo_sigmoid_gate.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int]
+        L.rdo_rms_norm.restype = None
+        L.rdo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float]
         L.rdo_deinterleave_q_gate.restype = None
         L.rdo_deinterleave_q_gate.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int]
         L.rdo_attn.restype = C.c_int
@@ -155,6 +157,15 @@ class Oracle(_AttnMixin):
         y = _f32(y).copy()
         self.lib.rdo_sigmoid_gate(_ptr(g), _ptr(y), g.size, 1 if store_sigmoid else 0)
         return g, y
+
+    def rms_norm(self, x, w, eps):
+        """x [rows][cols] f32, w [cols] or None."""
+        x = _f32(x)
+        y = np.empty_like(x)
+        rows, cols = x.reshape(-1, x.shape[-1]).shape
+        wp = _ptr(_f32(w)) if w is not None else None
+        self.lib.rdo_rms_norm(_ptr(x), wp, _ptr(y), rows, cols, eps)
+        return y
 
     def deinterleave_q_gate(self, yq, n_tok, n_head, head_dim):
         yq = _f32(yq)
@@ -280,6 +291,15 @@ class Reference(_AttnMixin):
         y = _f32(y).copy()
         self.lib.ref_sigmoid_gate(_ptr(g), _ptr(y), g.size)
         return g, y
+
+    def rms_norm(self, x, w, eps):
+        x = _f32(x)
+        y = np.full_like(x, np.nan)
+        rows, cols = x.reshape(-1, x.shape[-1]).shape
+        wp = _ptr(_f32(w)) if w is not None else None
+        self.lib.ref_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float]
+        assert self.lib.ref_rms_norm(_ptr(x), wp, _ptr(y), rows, cols, eps) == 0
+        return y
 
     def attn(self, q, k, v, t, n_head_kv, scale, kt, vt):
         q = _f32(q)

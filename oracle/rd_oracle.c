@@ -291,6 +291,28 @@ void rdo_sigmoid_gate(float *g, float *y, int64_t n, int store_sigmoid) {
   }
 }
 
+/* include/rdna4/nn.cuh:23-63: y = x * rsqrt(mean(x^2) + eps) (* w). The sum of squares
+ * follows the kernel's order exactly: thread t accumulates elements t, t+256, ... with
+ * fmaf, then a shared-memory tree adds partial[t + stride] into partial[t] for stride =
+ * 128 .. 1. rsqrt is written as 1/sqrt (the device intrinsic is approximate; this is the
+ * value the tests hold the CUDA kernel to). x and y may alias. */
+void rdo_rms_norm(const float *x, const float *w, float *y, int64_t nrows, int64_t ncols, float eps) {
+  for (int64_t r = 0; r < nrows; ++r) {
+    const float *xr = x + r * ncols;
+    float *yr = y + r * ncols;
+    float partial[256];
+    for (int t = 0; t < 256; ++t) {
+      float acc = 0.0f;
+      for (int64_t i = t; i < ncols; i += 256) acc = fmaf(xr[i], xr[i], acc);
+      partial[t] = acc;
+    }
+    for (int stride = 128; stride > 0; stride >>= 1)
+      for (int t = 0; t < stride; ++t) partial[t] += partial[t + stride];
+    const float scale = 1.0f / sqrtf(partial[0] / (float)ncols + eps);
+    for (int64_t i = 0; i < ncols; ++i) yr[i] = w ? xr[i] * scale * w[i] : xr[i] * scale;
+  }
+}
+
 /* include/rdna4/gdn.cuh:367-375,838-851: per head [q(hd) | gate(hd)] -> q, gate. */
 void rdo_deinterleave_q_gate(const float *yq, float *q, float *gate, int64_t n_tok, int n_head,
                              int head_dim) {

@@ -259,6 +259,13 @@ int ref_rope(float *x, int n_tok, int n_heads, int head_dim, int n_rot, float fr
   return 0;
 }
 
+// rms_norm_launch (nn.cuh:94-101): one block of 256 threads per row.
+int ref_rms_norm(const float *x, const float *w, float *y, int64_t nrows, int64_t ncols, float eps) {
+  run_grid(dim3((unsigned)nrows), rdna4::kRmsNormThreads,
+           [&] { rdna4::rms_norm_kernel(x, w, y, ncols, eps); });
+  return 0;
+}
+
 // sigmoid_gate_launch (nn.cuh:414-420).
 int ref_sigmoid_gate(float *g_io, float *y_io, int64_t n) {
   run_grid_nosync(dim3((unsigned)((n + 255) / 256)), 256,

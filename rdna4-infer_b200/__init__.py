@@ -39,6 +39,9 @@ SIGNATURES = {
     "rd_rope": (_I, [_P, _I, _I, _I, _I, _F, _P, _P]),
     "rd_deinterleave_q_gate": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "rd_sigmoid_gate": (_I, [_P, _P, _L, _P]),
+    "rd_rms_norm": (_I, [_P, _P, _P, _L, _L, _F, _P]),
+    "rd_pre_attn_fused": (_I, [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I,
+                               _F, _P]),
     "rd_attn_partial_bytes": (C.c_size_t, [_I, _I, _I]),
     "rd_attn_workspace_bytes": (C.c_size_t, [_I, _I, _I]),
     "rd_attn_decode": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P]),

@@ -319,6 +319,38 @@ int rd_sigmoid_gate(float *g_io, float *y_io, int64_t n, void *stream) {
   return launch_sigmoid_gate(g_io, y_io, n, (cudaStream_t)stream);
 }
 
+int rd_rms_norm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n_cols, float eps,
+                void *stream) {
+  if (n_rows < 0 || n_cols < 1) return RD_ERR_SHAPE;
+  if (n_rows == 0) return RD_OK;
+  if (x == nullptr || y == nullptr) return RD_ERR_NULL;
+  if (!aligned(x, 4) || !aligned(y, 4) || !aligned(w, 4)) return RD_ERR_ALIGN;
+  return launch_rms_norm(x, w, y, n_rows, n_cols, eps, (cudaStream_t)stream);
+}
+
+int rd_pre_attn_fused(const float *q_gate, const float *k_src, const float *v_src,
+                      const float *q_norm_w, const float *k_norm_w, float eps, float *q_out,
+                      float *gate_out, void *k_rows, void *v_rows, int k_type, int v_type,
+                      const int32_t *pos, int n_tok, int n_head, int n_head_kv, int head_dim,
+                      int n_rot, float freq_base, void *stream) {
+  if (!known_type(k_type) || !known_type(v_type)) return RD_ERR_TYPE;
+  if (n_tok < 0 || n_head < 1 || n_head_kv < 1 || head_dim < 32 || head_dim % 32 != 0)
+    return RD_ERR_SHAPE;
+  if (n_rot < 0 || n_rot > head_dim) return RD_ERR_SHAPE;
+  if (head_dim != kHeadDim || n_rot % 64 != 0) return RD_ERR_UNSUPPORTED;
+  if (n_tok == 0) return RD_OK;
+  if (q_gate == nullptr || k_src == nullptr || v_src == nullptr || q_out == nullptr ||
+      gate_out == nullptr || k_rows == nullptr || v_rows == nullptr || pos == nullptr)
+    return RD_ERR_NULL;
+  if (!aligned(q_gate, 4) || !aligned(k_src, 4) || !aligned(v_src, 4) || !aligned(q_out, 4) ||
+      !aligned(gate_out, 4) || !aligned(q_norm_w, 4) || !aligned(k_norm_w, 4) || !aligned(pos, 4))
+    return RD_ERR_ALIGN;
+  if (!aligned(k_rows, 4) || !aligned(v_rows, 4)) return RD_ERR_ALIGN;
+  return launch_pre_attn(k_type, v_type, q_gate, k_src, v_src, q_norm_w, k_norm_w, eps, q_out,
+                         gate_out, k_rows, v_rows, pos, n_tok, n_head, n_head_kv, n_rot, freq_base,
+                         (cudaStream_t)stream);
+}
+
 size_t rd_attn_partial_bytes(int n_head, int head_dim, int n_splits) {
   if (n_head < 0 || head_dim < 0 || n_splits < 0) return 0;
   return (size_t)n_head * (size_t)n_splits * (2 + (size_t)head_dim) * sizeof(float);

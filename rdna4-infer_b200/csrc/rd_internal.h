@@ -20,6 +20,16 @@ int launch_deinterleave(const float *yq, float *q, float *gate, int64_t n_rows, 
                         cudaStream_t st);
 int launch_sigmoid_gate(float *g, float *y, int64_t n, cudaStream_t st);
 
+// ---- rd_pre.cu
+int launch_rms_norm(const float *x, const float *w, float *y, int64_t nrows, int64_t ncols, float eps,
+                    cudaStream_t st);
+// One launch for deinterleave + q/k RMS-norm + RoPE + K/V quantize-and-store of n_tok
+// tokens (head_dim 256, n_rot a multiple of 64).
+int launch_pre_attn(int kt, int vt, const float *qg, const float *k_src, const float *v_src,
+                    const float *q_w, const float *k_w, float eps, float *q_out, float *gate_out,
+                    void *k_rows, void *v_rows, const int32_t *pos, int n_tok, int n_head, int nkv,
+                    int n_rot, float freq_base, cudaStream_t st);
+
 // ---- rd_decode_*.cu
 // One launch of the split-KV decode kernel: grid (n_splits, n_tok). Token i attends
 // keys key_begin..(pos ? pos[i] : t). Writes n_splits records per (token, head) into

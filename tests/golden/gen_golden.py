@@ -3,7 +3,7 @@
 Every expected value here is produced by the REFERENCE project's own kernels
 (kv_store_row_kernel, rope_kernel, attn_kernel, attn_split_kernel,
 attn_merge_kernel, attn_batch_kernel, attn_split_batch_kernel,
-attn_fa2_prefill_kernel, sigmoid_gate_kernel and the fp16 helpers), executed on the
+attn_fa2_prefill_kernel, sigmoid_gate_kernel, rms_norm_kernel and the fp16 helpers), executed on the
 CPU by oracle/_ref/librd_ref.so. It therefore only runs where the reference checkout
 is present (``make -C oracle ref``); the .npz files it writes are committed and are
 what the tests read.
@@ -46,8 +46,28 @@ def hostile_rows(rng):
     return rows
 
 
+def gen_rms_norm(ref):
+    """rms_norm_kernel (nn.cuh:23-63) on head-sized rows (the q/k norm of the attention
+    layers) and on a 5120-wide row (20 elements per thread), with and without weights."""
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((9, HD)).astype(np.float32)
+    x[3] = 0.0
+    x[4] *= 1e-4
+    x[5] *= 300.0
+    w = (1.0 + 0.1 * rng.standard_normal(HD)).astype(np.float32)
+    xw = rng.standard_normal((2, 5120)).astype(np.float32)
+    ww = (1.0 + 0.1 * rng.standard_normal(5120)).astype(np.float32)
+    np.savez(os.path.join(HERE, "rms_norm.npz"), x=x, w=w, eps=np.float32(1e-6),
+             y_w=ref.rms_norm(x, w, 1e-6), y_now=ref.rms_norm(x, None, 1e-6),
+             xw=xw, ww=ww, yw=ref.rms_norm(xw, ww, 1e-5))
+
+
 def main():
     ref = Reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "rms_norm":   # only this file (keeps the others' bytes)
+        gen_rms_norm(ref)
+        return
+    gen_rms_norm(ref)
     rng = np.random.default_rng(20250916)
 
     # ---- fp16 conversion: a spread of magnitudes incl. subnormal/overflow edges

@@ -141,3 +141,13 @@ def test_empty_and_edge_cases(oracle):
     assert np.isneginf(part[:, :, 0]).all() and (part[:, :, 1:] == 0).all()
     with pytest.raises(ValueError):
         oracle.kv_store_rows(Q4_0, np.zeros(33, dtype=np.float32))
+
+
+def test_rms_norm_bit_exact(oracle, golden):
+    """rms_norm_kernel (nn.cuh:23-63): same fmaf chain per thread, same reduction tree."""
+    g = golden("rms_norm")
+    eps = float(g["eps"])
+    assert np.array_equal(oracle.rms_norm(g["x"], g["w"], eps), g["y_w"])
+    assert np.array_equal(oracle.rms_norm(g["x"], None, eps), g["y_now"])
+    assert np.array_equal(oracle.rms_norm(g["xw"], g["ww"], 1e-5), g["yw"])
+    assert (g["y_w"][3] == 0).all()          # an all-zero row stays zero (eps > 0)
