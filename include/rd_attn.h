@@ -129,6 +129,21 @@ int rd_pre_attn_fused(const float *q_gate, const float *k_src, const float *v_sr
                       const int32_t *pos, int n_tok, int n_head, int n_head_kv, int head_dim,
                       int n_rot, float freq_base, void *stream);
 
+/* ---- split policy. rd_attn_splits_for is the reference's rule for how many partial
+ * records per head a caller allocates (Graph::attn_splits_for, graph.cuh:495-526, constants
+ * of tuning.h:144-150): 1 below 512 keys; ceil(96 / n_head) for f16 / f32 caches;
+ * min(16, n_keys / 512) for quantized ones; forced > 0 overrides (the RD_ATTN_SPLITS
+ * knob), capped at 16. Host arithmetic only.
+ *
+ * rd_attn_plan reports what THIS library does with a decode launch on a GPU of sm_count
+ * SMs (<= 0: the current device): keys per shared-memory tile (16, 32 or 48 by K / V type),
+ * stages of the TMA ring, and the internal split count (about one CTA per SM, never more
+ * splits than key tiles). Any output pointer may be NULL. Host arithmetic only when
+ * sm_count is given. */
+int rd_attn_splits_for(int n_keys, int k_type, int v_type, int n_head, int forced);
+int rd_attn_plan(int n_keys, int n_tok, int n_head_kv, int k_type, int v_type, int sm_count,
+                 int *tile_keys, int *ring_stages, int *n_splits);
+
 /* ---- partial records: attn_partial_bytes, include/rdna4/attn.cuh:665-667.
  * A record is (m, l, acc[head_dim]) f32 in natural-log units: m = max scaled score,
  * l = sum exp(s - m), acc = sum exp(s - m) * v; an empty record is (-inf, 0, 0...). */

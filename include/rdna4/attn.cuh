@@ -61,6 +61,11 @@ inline std::size_t attn_partial_bytes(int n_head, int head_dim, int n_splits) {
 }
 
 // attn.cuh:895-901 (shape policy of the reference's split kernel; informational here)
+// Graph::attn_splits_for (graph.cuh:495-526) as a free function: the split count a caller
+// sizes its partial buffer for (the library plans its own internal split, rd_attn_plan).
+inline int attn_splits_for(int keys, KvType kt, KvType vt, int n_head, int forced = 0) {
+  return rd_attn_splits_for(keys, (int)kt, (int)vt, n_head, forced);
+}
 inline int attn_split_wpb(int n_splits) {
   if (n_splits <= kAttnSplitWpbLimit) return 16;
   if (n_splits >= kAttnSplitWpbWide) return 16;

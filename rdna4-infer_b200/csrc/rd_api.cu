@@ -351,6 +351,43 @@ int rd_pre_attn_fused(const float *q_gate, const float *k_src, const float *v_sr
                          (cudaStream_t)stream);
 }
 
+int rd_attn_splits_for(int n_keys, int k_type, int v_type, int n_head, int forced) {
+  // Graph::attn_splits_for (graph.cuh:495-526) with the constants of tuning.h:144-150
+  constexpr int kSplitMin = 512, kMaxSplits = 16, kCtasDense = 96;
+  if (!known_type(k_type) || !known_type(v_type)) return RD_ERR_TYPE;
+  if (n_keys < 0 || n_head < 1) return RD_ERR_SHAPE;
+  if (forced > 0) return forced > kMaxSplits ? kMaxSplits : forced;
+  if (n_keys < kSplitMin) return 1;
+  const bool dense = (k_type == RD_KV_F16 || k_type == RD_KV_F32) &&
+                     (v_type == RD_KV_F16 || v_type == RD_KV_F32);
+  int sp = dense ? (kCtasDense + n_head - 1) / n_head : n_keys / kSplitMin;
+  if (sp < 1) sp = 1;
+  return sp > kMaxSplits ? kMaxSplits : sp;
+}
+
+int rd_attn_plan(int n_keys, int n_tok, int n_head_kv, int k_type, int v_type, int sm_count,
+                 int *tile_keys, int *ring_stages, int *n_splits) {
+  if (!known_type(k_type) || !known_type(v_type)) return RD_ERR_TYPE;
+  if (n_keys < 0 || n_tok < 1) return RD_ERR_SHAPE;
+  if (n_head_kv != 1 && n_head_kv != 2 && n_head_kv != 4) return RD_ERR_UNSUPPORTED;
+  if (sm_count <= 0) {
+    int dev;
+    const int rc = current_device(&dev);
+    if (rc != RD_OK) return rc;
+    sm_count = ::sm_count(dev);
+  }
+  const int tile = decode_tile_keys(k_type, v_type);
+  const int stage_bytes = tile * (key_pitch(k_type, n_head_kv) + key_pitch(v_type, n_head_kv));
+  int stages = (kSmemBudget - kRingOffset) / stage_bytes;
+  if (stages < 1) return RD_ERR_UNSUPPORTED;
+  if (stages > kMaxStages) stages = kMaxStages;
+  const int64_t tiles = ((int64_t)n_keys + tile - 1) / tile;
+  if (tile_keys != nullptr) *tile_keys = tile;
+  if (ring_stages != nullptr) *ring_stages = stages;
+  if (n_splits != nullptr) *n_splits = plan_splits(sm_count, n_tok, tiles);
+  return RD_OK;
+}
+
 size_t rd_attn_partial_bytes(int n_head, int head_dim, int n_splits) {
   if (n_head < 0 || head_dim < 0 || n_splits < 0) return 0;
   return (size_t)n_head * (size_t)n_splits * (2 + (size_t)head_dim) * sizeof(float);
