@@ -1,6 +1,7 @@
 // Shared device/host helpers of the sm_100a attention / KV-cache library.
 #pragma once
 #include <math.h>
+#include <stdlib.h>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -77,6 +78,41 @@ __host__ __device__ constexpr int key_groups(int kt, int vt) {
 // Floats of one warp's slot in the epilogue staging: 6 heads x (m, l, 8 blocks x 33).
 constexpr int kStgHead = 2 + 8 * 33;
 constexpr int kStgWarp = kGroup * kStgHead;
+
+// ---- programmatic dependent launch ---------------------------------------------
+// The hot kernels of a layer step (append, decode, merge) are launched with the
+// programmatic-stream-serialization attribute: the next kernel of the stream may be
+// scheduled while this one still runs, so its launch latency and its memory-independent
+// set-up overlap this kernel's tail. Every such kernel calls pdl_launch_dependents() first
+// (the kernel after it may start launching) and pdl_wait() before its first access to
+// global memory (the kernel before it has completed and its writes are visible).
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline int pdl_mask() {
+  static const int m = [] {
+    const char *e = getenv("RD_PDL");
+    return e ? atoi(e) : 2;   // measured: only the decode kernel gains as a dependent launch
+  }();
+  return m;
+}
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(int which, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl_mask() & which) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---- PTX helpers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

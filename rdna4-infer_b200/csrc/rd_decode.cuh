@@ -472,6 +472,7 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
 
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
+  pdl_launch_dependents();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -496,6 +497,15 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const uint8_t *kbase, *vbase;
   const CUtensorMap *tmk, *tmv;
   float *rec0;
+  if (threadIdx.x == 0) {   // barriers first: they need nothing from global memory
+    s_abort = 0;
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, CW);
+    }
+    fence_barrier_init();
+  }
+  pdl_wait();   // everything below reads what earlier kernels of the stream wrote
   if constexpr (MULTI) {
     const int4 item = p.items[blockIdx.x];
     const DecodeSeq &d = p.seqs[item.x];
@@ -534,14 +544,6 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const int ntiles = tile_e - tile_b;
   const int key0 = key_begin + tile_b * TILE;
 
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    for (int i = 0; i < p.stages; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, CW);
-    }
-    fence_barrier_init();
-  }
   __syncthreads();
   if (warp < CW) {
     // Query rows of this token -> shared memory, pre-scaled into log2 units (and by the
@@ -851,14 +853,34 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     out[1] = ll;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < n_heads_cta * kHeadDim; idx += blockDim.x) {
-    const int h = idx >> 8, d = idx & 255;
-    const int hk = h / kGroup, hh = h % kGroup;
-    const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
-    float acc = 0.f;
+  const size_t head_stride = (size_t)S * kRec;
+  if ((reinterpret_cast<uintptr_t>(rec0) & 7) == 0) {
+    // records are 8-byte aligned (always true for the library's own workspace): two dims
+    // per thread and store
+#pragma unroll 2
+    for (int idx = threadIdx.x; idx < n_heads_cta * (kHeadDim / 2); idx += blockDim.x) {
+      const int h = idx >> 7, d = 2 * (idx & 127);
+      const int hk = h / kGroup, hh = h % kGroup;
+      const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
+      float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < KG; ++w) acc += stg[(w * nkv + hk) * kStgWarp + off] * s_wgt[w][h];
-    rec0[(size_t)h * S * kRec + 2 + d] = acc;
+      for (int w = 0; w < KG; ++w) {
+        const float wg = s_wgt[w][h];
+        a0 += stg[(w * nkv + hk) * kStgWarp + off] * wg;
+        a1 += stg[(w * nkv + hk) * kStgWarp + off + 1] * wg;
+      }
+      *reinterpret_cast<float2 *>(rec0 + h * head_stride + 2 + d) = make_float2(a0, a1);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < n_heads_cta * kHeadDim; idx += blockDim.x) {
+      const int h = idx >> 8, d = idx & 255;
+      const int hk = h / kGroup, hh = h % kGroup;
+      const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < KG; ++w) acc += stg[(w * nkv + hk) * kStgWarp + off] * s_wgt[w][h];
+      rec0[h * head_stride + 2 + d] = acc;
+    }
   }
 }
 
@@ -930,8 +952,10 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.debug = decode_debug_mask();
   k.status = a.status;
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
-  decode_kernel<KT, VT, false><<<grid, (4 * KG + 1) * 32, smem, st>>>(k);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3((4 * KG + 1) * 32), smem, st, k) ==
+                 cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
 }
 
 // Multi-sequence flavour: fills the tensor maps of the host-side descriptors (prepare)
@@ -967,8 +991,10 @@ int multi_decode_typed(const MultiDecodeArgs &a, cudaStream_t st) {
   k.seqs = a.dev_seqs;
   k.items = a.dev_items;
   k.q_len = a.q_len;
-  decode_kernel<KT, VT, true><<<(unsigned)a.n_items, (4 * KG + 1) * 32, smem, st>>>(k);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return launch_pdl(2, decode_kernel<KT, VT, true>, dim3((unsigned)a.n_items), dim3((4 * KG + 1) * 32),
+                    smem, st, k) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
 }
 
 }  // namespace rd

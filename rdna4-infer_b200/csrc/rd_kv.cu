@@ -43,6 +43,8 @@ kv_append_kernel(const float *__restrict__ ksrc, const float *__restrict__ vsrc,
   // the n_rot/2 frequencies once per CTA (a double pow per element would dominate a
   // 512-token append)
   __shared__ float s_freq[kMaxRopePairs];
+  pdl_launch_dependents();
+  pdl_wait();
   if (pos != nullptr && blockIdx.y == 0 && (int)threadIdx.x < n_rot / 2)
     s_freq[threadIdx.x] = (int)threadIdx.x < kRopeTablePairs ? tab.f[threadIdx.x]
                                                              : rope_freq(freq_base, threadIdx.x, n_rot);
@@ -144,10 +146,11 @@ static int append_dispatch_v(int vt, const float *ks, const float *vs, uint8_t *
                              int n_rot, float freq_base, cudaStream_t st) {
   const dim3 grid((unsigned)((n_blocks * 32 + 255) / 256), 2);
   const RopeTable tab = make_rope_table(pos != nullptr ? n_rot : 0, freq_base);
+  cudaError_t err = cudaSuccess;
 #define RD_V(VT)                                                                              \
   case VT:                                                                                    \
-    kv_append_kernel<KT, VT><<<grid, 256, 0, st>>>(ks, vs, kd, vd, n_blocks, head_dim,        \
-                                                   heads_per_tok, pos, n_rot, freq_base, tab); \
+    err = launch_pdl(1, kv_append_kernel<KT, VT>, grid, dim3(256), 0, st, ks, vs, kd, vd, n_blocks, \
+                     head_dim, heads_per_tok, pos, n_rot, freq_base, tab);                      \
     break;
   switch (vt) {
     RD_V(RD_KV_F32)
@@ -159,7 +162,7 @@ static int append_dispatch_v(int vt, const float *ks, const float *vs, uint8_t *
     default: return RD_ERR_TYPE;
   }
 #undef RD_V
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return err == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 
 int launch_kv_append(int kt, int vt, const float *ks, const float *vs, void *kd, void *vd,

@@ -26,6 +26,8 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
   __shared__ float s_l[kMergeGroups];
   __shared__ float s_acc[kMergeGroups][kMergeDims];
   __shared__ float s_mm;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int row = blockIdx.x;
   const int quarter = blockIdx.y;
@@ -109,18 +111,20 @@ int launch_merge(const float *partial, float *out, int n_rows, int n_splits, flo
                  cudaStream_t st) {
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, 1);
-  merge_kernel<0><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, out, n_splits, 1, gate,
-                                                              nullptr, 1);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return launch_pdl(4, merge_kernel<0>, grid, dim3(kMergeDims * kMergeGroups), 0, st, partial, out, n_splits,
+                    1, gate, nullptr, 1) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
 }
 
 int launch_merge_records(const float *partial, float *records, int n_rows, int n_in, int n_out,
                          cudaStream_t st) {
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, (unsigned)n_out);
-  merge_kernel<1><<<grid, kMergeDims * kMergeGroups, 0, st>>>(partial, records, n_in, n_out,
-                                                               nullptr, nullptr, 1);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return launch_pdl(4, merge_kernel<1>, grid, dim3(kMergeDims * kMergeGroups), 0, st, partial, records, n_in,
+                    n_out, nullptr, nullptr, 1) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
 }
 
 int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_seq, int q_len,
@@ -128,9 +132,10 @@ int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_se
   const int rows = n_seq * q_len * n_head;
   if (rows == 0) return RD_OK;
   const dim3 grid((unsigned)rows, kHeadDim / kMergeDims, 1);
-  merge_kernel<2><<<grid, kMergeDims * kMergeGroups, 0, st>>>(records, nullptr, 0, 1, nullptr,
-                                                              dev_seqs, q_len * n_head);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  return launch_pdl(4, merge_kernel<2>, grid, dim3(kMergeDims * kMergeGroups), 0, st, records, nullptr, 0, 1,
+                    nullptr, dev_seqs, q_len * n_head) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
 }
 
 }  // namespace rd
