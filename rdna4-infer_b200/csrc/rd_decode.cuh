@@ -545,19 +545,37 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const int key0 = key_begin + tile_b * TILE;
 
   __syncthreads();
+  // Query fragments. Lane (g, tq) of every consumer warp of a kv head needs the same 32
+  // words: head g's values at the dims KL::dim(tq, n, 0..3), n = 0..15, as f16 pairs
+  // pre-scaled into log2 units (and by the loader's fixed-point factor). The consumer
+  // threads build them cooperatively: a 256-entry table inverts KL::dim (dim -> fragment
+  // slot), every thread then loads query values coalesced and drops each as an f16 into
+  // its slot, 144 bytes per (head, tq), and every lane reads its 32 words with 8
+  // conflict-free 16-byte loads -- instead of 64 scalar gathers per lane, repeated by
+  // every key-group warp.
+  constexpr int kFragPitch = 144;   // bytes per (head, tq): 32 words + 16 of padding
+  unsigned short *inv = reinterpret_cast<unsigned short *>(qstage);           // 512 bytes
+  const uint32_t frag0 = smem_u32(qstage) + 512;
   if (warp < CW) {
-    // Query rows of this token -> shared memory, pre-scaled into log2 units (and by the
-    // loader's fixed-point factor), coalesced; the producer warp is already streaming.
+    for (int i = threadIdx.x; i < 256; i += CW * 32) {
+      const int tq_i = i >> 6, n_i = (i >> 2) & 15, e_i = i & 3;
+      // byte offset of the half inside the (head, tq) block: word 2n + (e >> 1), half e & 1
+      inv[KL::dim(tq_i, n_i, e_i)] = (unsigned short)(tq_i * kFragPitch + (2 * n_i + (e_i >> 1)) * 4 +
+                                                      (e_i & 1) * 2);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
     const float qmul = p.qscale * KL::kUnscale;
     const float4 *q4 = reinterpret_cast<const float4 *>(qsrc);
     for (int i = threadIdx.x; i < nkv * kGroup * (kHeadDim / 4); i += CW * 32) {
       const int head = i >> 6, c4 = i & 63;
       const float4 v = q4[i];
-      float *dst = qstage + head * kQRowFloats + 4 * c4 + (c4 >> 4);
-      dst[0] = v.x * qmul;
-      dst[1] = v.y * qmul;
-      dst[2] = v.z * qmul;
-      dst[3] = v.w * qmul;
+      const uint32_t hb = frag0 + (uint32_t)head * (4 * kFragPitch);
+      const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned short hbits = __half_as_ushort(__float2half_rn(x[j] * qmul));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(hb + inv[4 * c4 + j]), "h"(hbits) : "memory");
+      }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
   }
@@ -621,20 +639,18 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     }
   } else if (active) {
     // =========================== consumers ======================================
-    // Q fragments (B operand), pre-scaled into log2 units: lane (g, t) holds head g.
+    // Q fragments (B operand): lane (g, tq) holds head g's 32 words; padding heads are 0.
     uint32_t qb[16][2];
     {
-      const float *qrow = qstage + (kvh * kGroup + (g < kGroup ? g : 0)) * kQRowFloats;
+      const uint32_t fa =
+          frag0 + (uint32_t)((kvh * kGroup + (g < kGroup ? g : 0)) * 4 + tq) * kFragPitch;
 #pragma unroll
-      for (int n = 0; n < 16; ++n) {
-        float e[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int dd = KL::dim(tq, n, j);
-          e[j] = g < kGroup ? qrow[dd + (dd >> 6)] : 0.f;
-        }
-        qb[n][0] = pack_h2(e[0], e[1]);
-        qb[n][1] = pack_h2(e[2], e[3]);
+      for (int i = 0; i < 8; ++i) {
+        const uint4 v = lds128(fa + 16 * i);
+        qb[2 * i][0] = g < kGroup ? v.x : 0u;
+        qb[2 * i][1] = g < kGroup ? v.y : 0u;
+        qb[2 * i + 1][0] = g < kGroup ? v.z : 0u;
+        qb[2 * i + 1][1] = g < kGroup ? v.w : 0u;
       }
     }
 
