@@ -266,6 +266,98 @@ def batched_leg(rd, torch, dist, rank, world, peak):
     return res
 
 
+def reference_kernel_leg(rd, torch, q_dev, n_keys):
+    """Reported beside the product numbers, never part of them: the reference project's OWN
+    GPU launchers, compiled unmodified for sm_100a (oracle/_ref/librd_ref_gpu.so, built where
+    the reference checkout is present), timed on this GPU next to the product on the same
+    caches. Only f16 caches: the reference's quantized loaders read 32-bit words at
+    block + 2, which an NVIDIA GPU rejects as a misaligned address, so the headline q4_0
+    shape cannot run through them here. Rows: decode over n_keys f16 keys (reference
+    policy: 4 splits) against this library's f16 decode, and the reference's FA2 prefill
+    kernel at the top of its admission window against this library's prefill kernel.
+    None if the library is absent."""
+    try:
+        from oracle.oracle import ReferenceGpu
+        ref = ReferenceGpu()
+    except Exception:
+        return None
+    L = rd.lib
+    n_caches = 4          # 4 x 537 MB of f16 K+V: no L2 reuse between launches
+    st = rd.stream_ptr()
+    kcs = [torch.empty(n_keys * NKV * 512, dtype=torch.uint8, device="cuda") for _ in range(n_caches)]
+    vcs = [torch.empty(n_keys * NKV * 512, dtype=torch.uint8, device="cuda") for _ in range(n_caches)]
+    for i in range(n_caches):
+        rd.check(L.rd_kv_fill(1, rd.ptr(kcs[i]), n_keys * NKV, HD, 300 + i, st))
+        rd.check(L.rd_kv_fill(1, rd.ptr(vcs[i]), n_keys * NKV, HD, 400 + i, st))
+    out = torch.empty(NH, HD, device="cuda")
+    part = torch.empty(NH, 16, 2 + HD, device="cuda")
+    ws_bytes = L.rd_attn_workspace_bytes(1, NH, HD)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    bytes_f16 = algorithmic_bytes(n_keys, 512, 512)
+
+    def theirs_decode():
+        s2 = rd.stream_ptr()
+        for i in range(n_caches):
+            if ref.lib.refgpu_attn_split(rd.ptr(q_dev[i]), rd.ptr(kcs[i]), rd.ptr(vcs[i]), rd.ptr(out),
+                                         rd.ptr(part), n_keys - 1, NH, NKV, HD, SCALE, 1, 1, 4, s2) != 0:
+                raise RuntimeError("reference attn_launch_split refused the shape")
+
+    def ours_decode():
+        s2 = rd.stream_ptr()
+        for i in range(n_caches):
+            rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[i]), rd.ptr(kcs[i]), rd.ptr(vcs[i]), rd.ptr(out), None, 0,
+                                         n_keys - 1, NH, NKV, HD, SCALE, 1, 1, 4, None, rd.ptr(ws), ws_bytes,
+                                         s2))
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    res = {"what": "the reference's own HIP kernels compiled unmodified for sm_100a vs this library, "
+                   "same f16 caches, same GPU (the reference's quantized loaders cannot run on NVIDIA)"}
+    try:
+        for name, fn in (("reference", theirs_decode), ("this_library", ours_decode)):
+            ms = timed(fn, 5) / n_caches
+            res[f"decode_f16_{n_keys}keys_{name}"] = {"us": ms * 1e3, "gbs": bytes_f16 / (ms * 1e-3) / 1e9}
+        del kcs, vcs
+        n_q, keys = 512, 8192
+        kc = torch.empty(keys * NKV * 512, dtype=torch.uint8, device="cuda")
+        vc = torch.empty_like(kc)
+        rd.check(L.rd_kv_fill(1, rd.ptr(kc), keys * NKV, HD, 11, st))
+        rd.check(L.rd_kv_fill(1, rd.ptr(vc), keys * NKV, HD, 22, st))
+        q = torch.randn(n_q, NH, HD, device="cuda")
+        o = torch.empty_like(q)
+        pos = torch.arange(keys - n_q, keys, dtype=torch.int32, device="cuda")
+        flops = 4 * HD * NH * sum(keys - n_q + t + 1 for t in range(n_q))
+
+        def theirs_prefill():
+            if ref.lib.refgpu_fa2_prefill(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(pos), n_q,
+                                          keys - 1, keys, NH, NKV, HD, SCALE, rd.stream_ptr()) != 0:
+                raise RuntimeError("reference fa2_prefill_launch refused the shape")
+
+        def ours_prefill():
+            rd.check(L.rd_fa2_prefill(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(pos), n_q, keys - 1,
+                                      keys, NH, NKV, HD, SCALE, rd.stream_ptr()))
+        for name, fn in (("reference", theirs_prefill), ("this_library", ours_prefill)):
+            ms = timed(fn, 5)
+            res[f"fa2_prefill_512q_8192keys_{name}"] = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12}
+    except Exception as e:   # a baseline row must never take the bench down
+        res["error"] = f"{type(e).__name__}: {e}"
+    return res
+
+
 def workload_config(n_gpus):
     return {"workload": "decode q_len=1, ctx 131072 (pos 131000 -> 131001 keys), 24Q/4KV heads, hd 256, "
                         "K,V q4_0, 16 layer caches per step",
@@ -532,6 +624,10 @@ def main():
     out["config"]["exchange"] = exchange
     if rank == 0 and world == 1:
         out["prefill"] = prefill_leg(rd, torch, peaks)
+    if rank == 0 and world == 1:
+        refk = reference_kernel_leg(rd, torch, q_dev, N_KEYS)
+        if refk is not None:
+            out["reference_kernels_on_this_gpu"] = refk
     batched = batched_leg(rd, torch, dist, rank, world, peak)
     if rank == 0:
         out["batched_decode"] = batched

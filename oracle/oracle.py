@@ -362,6 +362,26 @@ class Reference(_AttnMixin):
         return bool(self.lib.ref_fa2_prefill_usable(kt, vt, n_q, pos0, n_head, n_head_kv, head_dim))
 
 
+class ReferenceGpu:
+    """oracle/_ref/librd_ref_gpu.so: the reference project's own GPU launchers compiled
+    unmodified for sm_100a (ref_gpu_driver.cu). Takes raw device pointers (ints). Raises
+    FileNotFoundError where the library was not built (no reference checkout)."""
+
+    def __init__(self):
+        path = os.path.join(HERE, "_ref", "librd_ref_gpu.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        L = C.CDLL(path)
+        P, I, F = C.c_void_p, C.c_int, C.c_float
+        L.refgpu_attn.argtypes = [P, P, P, P, I, I, I, I, F, I, I, P]
+        L.refgpu_attn_split.argtypes = [P, P, P, P, P, I, I, I, I, F, I, I, I, P]
+        L.refgpu_fa2_prefill.argtypes = [P, P, P, P, P, I, I, I, I, I, I, F, P]
+        L.refgpu_kv_store_rows.argtypes = [I, P, P, I, P]
+        for f in (L.refgpu_attn, L.refgpu_attn_split, L.refgpu_fa2_prefill, L.refgpu_kv_store_rows):
+            f.restype = I
+        self.lib = L
+
+
 def lcg_stream(seed: int, n: int) -> np.ndarray:
     """The reference tests' generator (tests/check_rope_gpu.hip:36-39): s = s*1664525 +
     1013904223, value ((s>>8)/2^24 - 0.5)*2 in f32. Returns n values."""

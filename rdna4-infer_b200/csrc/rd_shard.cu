@@ -42,13 +42,15 @@ static_assert(sizeof(XHeader) <= kShardHeaderBytes, "exchange header");
 __device__ __forceinline__ float *xrecords(unsigned char *xbuf) {
   return reinterpret_cast<float *>(xbuf + kShardHeaderBytes);
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+// Polls use a relaxed system-scope load; one acquire fence after the last poll orders
+// the record reads behind it (an acquire load per poll costs a fence per poll).
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {
   uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void fence_acq_rel_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
@@ -132,10 +134,15 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      // the barrier ordered the CTA's stores before this fence; the flags follow it
+      // The barrier above ordered the CTA's record stores before this thread; one
+      // system-scope fence then covers all of them (release is cumulative), and the
+      // flags can go out as plain system-scope stores behind it.
       __threadfence_system();
       for (int r = 0; r < g.world; ++r)
-        st_release_sys(&reinterpret_cast<XHeader *>(g.x[r])->flag[par][g.rank][fidx], epoch);
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(
+                         &reinterpret_cast<XHeader *>(g.x[r])->flag[par][g.rank][fidx]),
+                     "r"(epoch)
+                     : "memory");
     }
   }
 
@@ -145,13 +152,15 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
       if ((int)threadIdx.x < g.world) {
         const uint32_t *f = &me->flag[par][threadIdx.x][fidx];
         const unsigned long long t0 = global_ns();
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-          if (global_ns() - t0 > g.wait_ns) {  // that rank never pushed: give up, report
+        unsigned polls = 0;
+        while ((int32_t)(ld_relaxed_sys(f) - epoch) < 0) {
+          // the clock is only consulted now and then: reading it costs as much as a poll
+          if ((++polls & 63u) == 0 && global_ns() - t0 > g.wait_ns) {  // that rank never pushed
             ok = false;
             break;
           }
-          __nanosleep(40);
         }
+        fence_acq_rel_sys();
       }
       ok = __all_sync(0xffffffffu, ok);
       if (threadIdx.x == 0) {
