@@ -218,7 +218,8 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
  * row, -1 for an empty slice) and the same q; every rank receives the full attention
  * output. Instead of a library all-gather between two merges, each rank's kernel
  * stores its per-head record (m, l, acc) directly into every rank's exchange buffer
- * over NVLink and raises a flag there; the final merge waits for the flags.
+ * over NVLink, every value tagged with the call's sequence number in the same 8-byte
+ * store; the final merge spins (bounded) on the tags of the values it needs.
  *
  *   group->xbuf[r]   rank r's exchange buffer AS MAPPED INTO THIS PROCESS (peer-mapped
  *                    or symmetric memory; xbuf[rank] is the local one), each

@@ -569,7 +569,7 @@ size_t rd_shard_xbuf_bytes(int n_head, int head_dim, int world) {
   if (n_head < 1 || n_head > kShardMaxHeads || head_dim != kHeadDim || world < 1 ||
       world > kShardMaxWorld)
     return 0;
-  return align256(kShardHeaderBytes + (size_t)2 * world * n_head * 4 * kXPart * sizeof(float));
+  return align256(kShardHeaderBytes + (size_t)2 * world * n_head * 4 * kXPart * 8);
 }
 
 // Validates a group and converts it; RD_OK or an error.

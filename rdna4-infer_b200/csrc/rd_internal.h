@@ -129,11 +129,12 @@ int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_se
 // ---- rd_shard.cu
 // Exchange buffers of a context-sharded group, as mapped into this process: x[r] is
 // rank r's buffer (x[rank] the local one): kShardHeaderBytes of header, then
-// [2 parities][world][n_head][4 dim quarters][kXPart] f32 record parts.
+// [2 parities][world][n_head][4 dim quarters][kXPart] record parts of 8-byte words
+// (f32 value, epoch).
 constexpr int kShardMaxWorld = 8;
 constexpr int kShardMaxHeads = 32;
 constexpr int kXPart = 2 + 64;  // (m, l) + one quarter of the accumulator
-constexpr size_t kShardHeaderBytes = 16384;
+constexpr size_t kShardHeaderBytes = 256;
 struct ShardPeers {
   unsigned char *x[kShardMaxWorld];
   int rank;

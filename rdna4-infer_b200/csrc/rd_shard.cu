@@ -4,23 +4,28 @@
 // the merge are attn_merge_kernel's, include/rdna4/attn.cuh:563-590.)
 //
 // Every rank owns an exchange buffer that all ranks can address:
-//   header   epoch, arrival counter, flag[parity][source rank][head][dim quarter]
-//   records  [parity][source rank][head][dim quarter][2 + 64] f32 (m, l, 64 acc values)
+//   header   epoch, arrival counter
+//   records  [parity][source rank][head][dim quarter][2 + 64] 8-byte words, each word =
+//            (f32 value, epoch it belongs to): m, l and 64 accumulator values
 // One sharded attention call on rank r is two launches on r's stream:
 //   1. the split-KV decode kernel over r's slice of the keys -> S records per head in
 //      the caller's workspace (rd_decode.cuh);
 //   2. shard_exchange_kernel<PUSH, MERGE>: CTA (head, quarter) reduces the S records to
-//      one, STORES ITS QUARTER INTO EVERY RANK'S buffer and then the call's epoch into
-//      that rank's flag (release, system scope); the same CTA then waits (bounded) until
-//      the local flags of all ranks show this epoch and merges the `world` records into
-//      its quarter of the output (optional fused sigmoid gate). The last CTA to finish
-//      advances the local epoch.
+//      one and STORES ITS QUARTER INTO EVERY RANK'S buffer, every value as one 8-byte
+//      (value, epoch) store; the same CTA then reads the `world` parts from its own
+//      buffer, each thread spinning (bounded) on its own words until they carry this
+//      call's epoch, and merges them into its quarter of the output (optional fused
+//      sigmoid gate). The last CTA to finish advances the local epoch.
+// Tagging every word with the epoch (the low-latency protocol of collective libraries)
+// needs no flag, no fence and no barrier between data and flag: an 8-byte store arrives
+// whole, so a word that shows the epoch IS the value. Measured on two B200s, a system
+// fence plus separate flags cost 5-7 us per call more.
 // A CTA waits only after it has pushed, and only for pushes, so no rank can block
 // another; a rank can run at most one call ahead of the slowest one (its next merge
-// needs that rank's next push), which is why two parities of records and flags are
-// enough. The epoch lives in device memory, not in a launch argument, so the same
-// launches can be replayed from a CUDA graph. The two halves also exist as separate
-// launches (PUSH only, MERGE only) for callers that compute the records themselves.
+// needs that rank's next push), which is why two parities of records are enough. The
+// epoch lives in device memory, not in a launch argument, so the same launches can be
+// replayed from a CUDA graph. The two halves also exist as separate launches (PUSH only,
+// MERGE only) for callers that compute the records themselves.
 #include "rd_common.cuh"
 #include "rd_internal.h"
 
@@ -33,37 +38,51 @@ constexpr int kQuarters = kHeadDim / kPushDims;
 struct XHeader {
   uint32_t epoch;        // calls completed on this rank
   uint32_t merge_count;  // CTAs of the running merge that are done
-  uint32_t pad_[62];
-  // [parity][source rank][head * 4 + dim quarter]: the epoch whose record part has landed
-  uint32_t flag[2][kShardMaxWorld][kShardMaxHeads * kQuarters];
 };
 static_assert(sizeof(XHeader) <= kShardHeaderBytes, "exchange header");
 
-__device__ __forceinline__ float *xrecords(unsigned char *xbuf) {
-  return reinterpret_cast<float *>(xbuf + kShardHeaderBytes);
+__device__ __forceinline__ uint2 *xwords(unsigned char *xbuf) {
+  return reinterpret_cast<uint2 *>(xbuf + kShardHeaderBytes);
 }
-// Polls use a relaxed system-scope load; one acquire fence after the last poll orders
-// the record reads behind it (an acquire load per poll costs a fence per poll).
-__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ void st_word_sys(uint2 *p, float v, uint32_t epoch) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
+               "r"(epoch)
+               : "memory");
+}
+__device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
-}
-__device__ __forceinline__ void fence_acq_rel_sys() {
-  asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+// Spins until the word carries `epoch`; false when wait_ns ran out first. The clock is
+// only consulted every 64 polls: reading it costs as much as a poll.
+__device__ __forceinline__ bool wait_word(const uint2 *p, uint32_t epoch, unsigned long long wait_ns,
+                                          float &value) {
+  uint2 w = ld_word_sys(p);
+  if (w.y != epoch) {
+    const unsigned long long t0 = global_ns();
+    unsigned polls = 0;
+    do {
+      if ((++polls & 63u) == 0 && global_ns() - t0 > wait_ns) return false;
+      w = ld_word_sys(p);
+    } while (w.y != epoch);
+  }
+  value = __uint_as_float(w.x);
+  return true;
+}
 
 // grid (n_head, 4 dim quarters), 1024 threads = 16 record groups x 64 dims. CTA (head,
 // quarter) handles that quarter of the head's record in both halves:
-//   PUSH : this rank's n_in split records -> one record, stored into every rank's buffer,
-//          then the epoch into every rank's flag for (this rank, head, quarter);
-//   MERGE: wait (bounded) for all ranks' flags of (head, quarter), combine the `world`
-//          records into the output quarter, count the CTA towards the epoch advance.
+//   PUSH : this rank's n_in split records -> one record part, stored into every rank's
+//          buffer as (value, epoch) words;
+//   MERGE: every thread of the first two warps waits (bounded) for its words of all
+//          ranks' parts, combines them into the output quarter, and the CTA counts
+//          towards the epoch advance.
 // A CTA never waits before it has pushed, so ranks cannot block one another.
 template <bool PUSH, bool MERGE>
 __global__ void __launch_bounds__(kPushDims *kPushGroups)
@@ -72,7 +91,6 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
   __shared__ float s_l[kPushGroups];
   __shared__ float s_acc[kPushGroups][kPushDims];
   __shared__ float s_mm;
-  __shared__ int s_ok;
 
   const int row = blockIdx.x, quarter = blockIdx.y;
   const int tx = threadIdx.x % kPushDims, ty = threadIdx.x / kPushDims;
@@ -80,7 +98,9 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
   XHeader *me = reinterpret_cast<XHeader *>(g.x[g.rank]);
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&me->epoch) + 1;
   const int par = epoch & 1;
-  const int fidx = row * kQuarters + quarter;
+  // word index of part (parity, source rank r, head row, quarter): + r * rstride
+  const size_t rstride = (size_t)n_head * kQuarters * kXPart;
+  const size_t part0 = (size_t)par * g.world * rstride + ((size_t)row * kQuarters + quarter) * kXPart;
 
   if (PUSH) {
     const float *base = partial + (size_t)row * n_in * kRec;
@@ -120,77 +140,52 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
         a += s_acc[i][tx];
         l += s_l[i];
       }
-      // every quarter carries its own copy of (m, l): slot layout [quarter][2 + 64]
-      const size_t slot =
-          ((((size_t)par * g.world + g.rank) * n_head + row) * kQuarters + quarter) * kXPart;
+      // every quarter carries its own copy of (m, l): part layout [m, l, 64 values]
+      const size_t mine = part0 + (size_t)g.rank * rstride;
       for (int r = 0; r < g.world; ++r) {
-        float *rec = xrecords(g.x[r]) + slot;
-        rec[2 + tx] = a;
+        uint2 *rec = xwords(g.x[r]) + mine;
+        st_word_sys(rec + 2 + tx, a, epoch);
         if (tx == 0) {
-          rec[0] = mm;
-          rec[1] = l;
+          st_word_sys(rec, mm, epoch);
+          st_word_sys(rec + 1, l, epoch);
         }
       }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      // The barrier above ordered the CTA's record stores before this thread; one
-      // system-scope fence then covers all of them (release is cumulative), and the
-      // flags can go out as plain system-scope stores behind it.
-      __threadfence_system();
-      for (int r = 0; r < g.world; ++r)
-        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(
-                         &reinterpret_cast<XHeader *>(g.x[r])->flag[par][g.rank][fidx]),
-                     "r"(epoch)
-                     : "memory");
     }
   }
 
   if (MERGE) {
-    if (threadIdx.x < 32) {
+    if (ty == 0) {
+      const uint2 *recs = xwords(g.x[g.rank]) + part0;
       bool ok = true;
-      if ((int)threadIdx.x < g.world) {
-        const uint32_t *f = &me->flag[par][threadIdx.x][fidx];
-        const unsigned long long t0 = global_ns();
-        unsigned polls = 0;
-        while ((int32_t)(ld_relaxed_sys(f) - epoch) < 0) {
-          // the clock is only consulted now and then: reading it costs as much as a poll
-          if ((++polls & 63u) == 0 && global_ns() - t0 > g.wait_ns) {  // that rank never pushed
-            ok = false;
-            break;
-          }
+      float m_r[kShardMaxWorld], l_r[kShardMaxWorld], a_r[kShardMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kShardMaxWorld; ++r) {
+        m_r[r] = -INFINITY;
+        l_r[r] = a_r[r] = 0.f;
+        if (r < g.world && ok) {
+          const uint2 *rec = recs + r * rstride;
+          ok = wait_word(rec, epoch, g.wait_ns, m_r[r]) && wait_word(rec + 1, epoch, g.wait_ns, l_r[r]) &&
+               wait_word(rec + 2 + tx, epoch, g.wait_ns, a_r[r]);
         }
-        fence_acq_rel_sys();
       }
       ok = __all_sync(0xffffffffu, ok);
-      if (threadIdx.x == 0) {
-        s_ok = ok ? 1 : 0;
-        if (!ok && status != nullptr && atomicExch(&status->timeout_flag, 1) == 0)
-          status->where = 100 + g.rank;
-      }
-    }
-    __syncthreads();
-    if (ty == 0) {
-      float o = 0.f;
-      if (s_ok) {
-        const float *recs = xrecords(g.x[g.rank]) +
-                            (((size_t)par * g.world * n_head + row) * kQuarters + quarter) * kXPart;
-        const size_t rstride = (size_t)n_head * kQuarters * kXPart;
-        float mm = -INFINITY;
-        for (int r = 0; r < g.world; ++r) mm = fmaxf(mm, __ldcg(recs + r * rstride));
-        float a = 0.f, l = 0.f;
-        if (mm != -INFINITY) {
-          for (int r = 0; r < g.world; ++r) {
-            const float *rec = recs + r * rstride;
-            const float w = expf(__ldcg(rec) - mm);
-            if (w > 0.f) {
-              a = fmaf(__ldcg(rec + 2 + tx), w, a);
-              l = fmaf(__ldcg(rec + 1), w, l);
-            }
+      if (!ok && tx == 0 && status != nullptr && atomicExch(&status->timeout_flag, 1) == 0)
+        status->where = 100 + g.rank;   // some rank never pushed: zeros, reported
+      float mm = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < kShardMaxWorld; ++r) mm = fmaxf(mm, m_r[r]);
+      float a = 0.f, l = 0.f;
+      if (mm != -INFINITY) {
+#pragma unroll
+        for (int r = 0; r < kShardMaxWorld; ++r) {
+          const float w = expf(m_r[r] - mm);   // 0 for an empty part (m = -inf)
+          if (w > 0.f) {
+            a = fmaf(a_r[r], w, a);
+            l = fmaf(l_r[r], w, l);
           }
         }
-        o = (mm != -INFINITY && l > 0.f) ? a / l : 0.f;
       }
+      float o = (ok && mm != -INFINITY && l > 0.f) ? a / l : 0.f;
       if (gate != nullptr) {
         float *gp = gate + (size_t)row * kHeadDim + d;
         const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
