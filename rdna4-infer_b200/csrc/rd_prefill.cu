@@ -1,34 +1,39 @@
 // Causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
 // Replaces attn_fa2_prefill_kernel (include/rdna4/attn_fa2.cuh:30-169 of the reference)
-// for f16 K/V caches. One CTA owns a tile of 128 query tokens of ONE query head. Tensor
-// memory (512 columns x 128 lanes, lane = query row) holds everything the tensor core
-// reads or writes except K and V:
+// for f16 K/V caches. One CTA owns a tile of 128 query tokens of ONE query head and walks
+// the keys in tiles of 128. Tensor memory (512 columns x 128 lanes, lane = query row):
 //   columns   0..255  O, the f32 output accumulator
-//   columns 256..383  Q as f16 pairs (the A operand of S = Q K^T, read from TMEM)
-//   columns 384..511  two score buffers of 64 f32 columns; the f16 P of a tile is
-//                     written over the first 32 columns of its buffer (the A operand of
-//                     O += P V, read from TMEM)
+//   columns 256..511  two score buffers of 128 f32 columns; the f16 P of a tile is written
+//                     over the first 64 columns of its buffer (the A operand of O += P V,
+//                     read from TMEM)
+// Shared memory (224 KB): Q as f16 in the K-major 128-byte-swizzled layout (64 KB), a ring
+// of six K chunks of [128 keys][64 dims] (96 KB) and a ring of two V units of 64 keys
+// (64 KB), all filled by TMA with the hardware 128B swizzle.
 //
-//   prologue   the 128 x 256 f32 query rows are loaded coalesced into a staging area,
-//              each thread takes its row: optional partial RoPE, scale*log2(e), f16,
-//              tcgen05.st into the Q columns;
-//   per 64-key tile j (K and V on separate 2-stage TMA rings, sub-tiles of
-//              [64 keys][64 dims], hardware 128B swizzle, one producer warp each):
-//     MMA warp   S = Q K_j^T         16 x tcgen05.mma M128 N64  K16 (A in TMEM, B K-major)
-//     8 warps    two threads per query row, 32 score columns each (row max exchanged
+//   prologue   the 128 x 256 f32 query rows -> optional partial RoPE, scale*log2(e), f16,
+//              swizzled into shared memory (8 warps, 16 rows each);
+//   per 128-key tile j:
+//     warp 9     S = Q K_j^T        16 x tcgen05.mma M128 N128 K16, four per K chunk, each
+//                                   chunk handed back to the TMA producer as soon as its
+//                                   four MMAs are done (N = 128 keeps the tensor core busy
+//                                   for as long as the 128 x 16 A slice takes to fetch)
+//     warps 0-7  two threads per query row, 64 score columns each (row max exchanged
 //                through shared memory): tcgen05.ld the scores, causal mask
-//                (key <= pos[r]), running max with LAZY rescale (the reference point
-//                only moves when a row's max grows by more than 2^8, so P stays below 256
-//                in f16 and O in TMEM is rarely touched), P -> f16 pairs, tcgen05.st
-//     MMA warp   O += P V_j           4 x tcgen05.mma M128 N256 K16 (A in TMEM, B = V
-//                                     MN-major)
+//                (key <= pos[r]), running max with LAZY rescale (the reference point only
+//                moves when a row's max grows by more than 2^8, so P stays below 256 in
+//                f16 and O in TMEM is rarely touched), P -> f16 pairs, tcgen05.st
+//     warp 11    O += P V_j          8 x tcgen05.mma M128 N256 K16 (A = P from TMEM, B = V
+//                                   MN-major), four per V unit
 //   epilogue   O / l (times sigmoid(gate) if asked) through a swizzled staging tile to
 //              coalesced f32 stores.
+// Warps 8 and 10 are the K and V TMA producers (separate warps: a lane parked in
+// mbarrier.try_wait parks its whole warp). The two contractions have their own issuing
+// threads because issuing a tcgen05.mma costs the issuing thread tens of cycles.
 //
 // Scores are double-buffered: the tensor core computes S of tile j+1 while the softmax
-// warps work on tile j. The tensor pipe executes in issue order, which is what makes the
-// in-place P safe: S of tile j+2 is issued after P V of tile j.
+// warps work on tile j. S of tile j+2 waits for P V of tile j, which reads the P that
+// lives in its buffer.
 //
 // Synchronisation is mbarriers only (TMA transaction counts, tcgen05.commit); every wait
 // is bounded and a timeout unwinds the CTA (TMEM is always freed). No cluster launch, no
@@ -42,18 +47,20 @@
 namespace rd {
 
 constexpr int kPfM = 128;                 // query rows per CTA
-constexpr int kPfN = 64;                  // keys per tile
-constexpr int kPfStages = 2;
-constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // staging (prologue, epilogue): 65536
-constexpr int kPfKVStageBytes = 2 * kPfN * kHeadDim * 2;   // K + V tile: 65536
-// 192 KB of dynamic shared memory (one CTA per SM: TMEM is allocated whole)
-constexpr int kPfSmemBytes = kPfQBytes + kPfStages * kPfKVStageBytes;
+constexpr int kPfN = 128;                 // keys per tile
+constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536 (also the epilogue staging)
+constexpr int kPfKChunkBytes = kPfN * 128;                 // [128 keys][64 dims] f16: 16384
+constexpr int kPfKSlots = 6;                               // 1.5 tiles of K in flight
+constexpr int kPfVUnitKeys = 64;
+constexpr int kPfVUnitBytes = kPfVUnitKeys * kHeadDim * 2; // 32768
+constexpr int kPfVSlots = 2;
+// 224 KB of dynamic shared memory + < 3 KB static = the 227 KB an sm_100 CTA may use
+constexpr int kPfSmemBytes = kPfQBytes + kPfKSlots * kPfKChunkBytes + kPfVSlots * kPfVUnitBytes;
 constexpr int kPfThreads = 384;           // 8 softmax warps, K TMA, S MMA, V TMA, PV MMA warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 0;            // columns [0, 256): output accumulator
-constexpr uint32_t kTmemQ = 256;          // columns [256, 384): the query tile as f16 pairs
-constexpr uint32_t kTmemS = 384;          // columns [384, 512): two score buffers of 64; the
-                                          // f16 P of a tile overwrites its first 32 columns
+constexpr uint32_t kTmemS = 256;          // columns [256, 512): two score buffers of 128; the
+                                          // f16 P of a tile overwrites its first 64 columns
 constexpr float kLazyThreshold = 8.0f;    // log2 units
 
 struct PrefillArgs {
@@ -84,6 +91,16 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], both behind shared-memory descriptors.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand lives in tensor memory (rows = lanes, two
 // f16 per 32-bit column), B behind a shared-memory descriptor.
@@ -156,24 +173,10 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
                : "memory");
 }
 
-// Barrier slots (8 bytes each) at the start of the aligned shared-memory block.
-// K and V tiles travel on separate rings: a K stage is free as soon as its S MMAs are
-// done (long before the tile's P V), so K loads run two tiles ahead.
-enum { kBarVFull = 0, kBarVFree = 2, kBarS = 4, kBarP = 6, kBarQ = 8, kBarKFull = 9, kBarKFree = 11,
-       kBarX = 13, kBarCount = 15 };
 
-// Build with -DRD_PREFILL_TRACE to accumulate clock64() spans of the per-tile phases of
-// one softmax thread and of the MMA thread of CTA (0,0) (development aid, off by default).
-#ifdef RD_PREFILL_TRACE
-__device__ unsigned long long g_pf_trace[32];
-#define RD_TR_DECL long long tr_t = clock64(); unsigned long long tr_acc[12] = {}
-#define RD_TR(i) do { const long long tr_n = clock64(); tr_acc[i] += (unsigned long long)(tr_n - tr_t); tr_t = tr_n; } while (0)
-#define RD_TR_OUT(base, n) do { if (blockIdx.x == 0 && blockIdx.y == 0) for (int tr_i = 0; tr_i < (n); ++tr_i) g_pf_trace[(base) + tr_i] = tr_acc[tr_i]; } while (0)
-#else
-#define RD_TR_DECL
-#define RD_TR(i)
-#define RD_TR_OUT(base, n)
-#endif
+// Barrier slots (8 bytes each).
+enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarX = 20,
+       kBarO = 22, kBarQ = 24, kBarCount = 25 };
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -198,23 +201,26 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     return;
   }
   const uint32_t sQ = base;
-  const uint32_t sKV = sQ + kPfQBytes;                    // stage s: K at +0, V at +32 KB
-  uint8_t *gQ = smem_raw + (base - smem_u32(smem_raw));   // generic pointer to sQ
+  const uint32_t sK = sQ + kPfQBytes;                       // slot s at + s * 16 KB
+  const uint32_t sV = sK + kPfKSlots * kPfKChunkBytes;      // slot s at + s * 32 KB
+  uint8_t *gQ = smem_raw;                                   // generic pointer to sQ
+  uint8_t *gV = smem_raw + kPfQBytes + kPfKSlots * kPfKChunkBytes;
   const uint32_t bars = smem_u32(s_bars);
 
   if (threadIdx.x == 0) {
     s_maxpos = -1;
     s_abort = 0;
-    for (int i = 0; i < kPfStages; ++i) {
-      mbar_init(bars + 8 * (kBarVFull + i), 1);
-      mbar_init(bars + 8 * (kBarVFree + i), 1);
+    for (int i = 0; i < kPfKSlots; ++i) {
       mbar_init(bars + 8 * (kBarKFull + i), 1);
       mbar_init(bars + 8 * (kBarKFree + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (kBarVFull + i), 1);
+      mbar_init(bars + 8 * (kBarVFree + i), 1);
       mbar_init(bars + 8 * (kBarS + i), 1);
       mbar_init(bars + 8 * (kBarP + i), 8);   // one elected lane per softmax warp
       mbar_init(bars + 8 * (kBarX + i), 8);
+      mbar_init(bars + 8 * (kBarO + i), 1);
     }
     mbar_init(bars + 8 * kBarQ, 8);          // one per prologue warp
     fence_barrier_init();
@@ -249,216 +255,234 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   const int maxpos = s_maxpos;
   const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
 
-  // ---- prologue: Q rows -> f16 pairs in tensor memory (the A operand of S = Q K^T) ----
-  // Two passes of two 64-dim chunks: all 8 warps load the chunks coalesced into a staging
-  // area ([128 rows][64 floats] per chunk, 16-byte piece q of row r at q ^ (r & 15)), then
-  // warps 0-3 take the even chunk and warps 4-7 the odd one: thread = row (= TMEM lane)
-  // reads its 64 values, rotates them (chunk 0 holds all n_rot <= 64 rotated dims),
-  // scales by scale*log2(e), packs and stores 32 columns with tcgen05.st.
+  // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-7, 16 rows each) ----
   if (warp < 8) {
-    const int r = threadIdx.x & (kPfM - 1), half_id = threadIdx.x >> 7;   // row, chunk parity
-    const int gr_me = row0 + r;
-    const float fpos = gr_me < p.n_q ? (float)p.pos[gr_me] : 0.f;
-    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-#pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
-      // 2 chunks x 128 rows x 16 pieces = 4096 pieces of 16 bytes, 16 per thread
-#pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int idx = i * 256 + (int)threadIdx.x;
-        const int cpar = idx >> 11, rr = (idx >> 4) & (kPfM - 1), q = idx & 15;
-        const int gr = row0 + rr;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gr < p.n_q)
-          v = *(reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim +
-                                                 64 * (2 * pass + cpar)) + q);
-        sts128(sQ + cpar * (kPfM * 256) + rr * 256 + ((q ^ (rr & 15)) << 4), __float_as_uint(v.x),
-               __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
+    // cos/sin of every (row, pair) of this warp's 16 rows -- lane = (row, half of the
+    // pairs) -- parked in the V ring (the V producer starts only after this prologue):
+    // 4 KB per warp
+    float2 *cs_tab = reinterpret_cast<float2 *>(gV) + warp * (16 * 32);
+    const int pairs = p.n_rot / 2;
+    if (pairs > 0) {
+      const int gr_l = row0 + warp * 16 + (lane & 15);
+      const float fpos = gr_l < p.n_q ? (float)p.pos[gr_l] : 0.f;
+      for (int i = (lane >> 4); i < pairs; i += 2) {
+        float c, s;
+        sincosf(fpos * s_freq[i], &s, &c);
+        cs_tab[(lane & 15) * 32 + i] = make_float2(c, s);
       }
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      float x[64];
+      __syncwarp();
+    }
+#pragma unroll 8
+    for (int rr = 0; rr < 16; ++rr) {
+      const int r = warp * 16 + rr;      // row inside the tile
+      const int gr = row0 + r;
+      float v[8];
+      if (gr < p.n_q) {
+        const float4 *src =
+            reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim) + 2 * lane;
+        const float4 a = src[0], b = src[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      } else {
 #pragma unroll
-      for (int q = 0; q < 16; ++q) {
-        const float4 v = *reinterpret_cast<const float4 *>(gQ + half_id * (kPfM * 256) + r * 256 +
-                                                           ((q ^ (r & 15)) << 4));
-        x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
       }
-      if (pass == 0 && half_id == 0 && p.n_rot > 0) {
-        const int half = p.n_rot / 2;   // 8, 16, 24 or 32 pairs: (i, i + half)
+      if (pairs > 0) {
+        // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
+        // l and l ^ (n_rot/16) at the same element index
+        const int half_lanes = p.n_rot / 16;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i < half) {
-            float c, sn;
-            sincosf(fpos * s_freq[i], &sn, &c);
-            // the partner index is a compile-time constant only for half == 32
-            const float x0 = x[i];
-            float x1 = 0.f;
-#pragma unroll
-            for (int k = 8; k <= 32; k += 8)
-              if (half == k) x1 = x[i + k];
-            const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
-            const float y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
-            x[i] = y0;
-#pragma unroll
-            for (int k = 8; k <= 32; k += 8)
-              if (half == k) x[i + k] = y1;
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
+          if (lane < 2 * half_lanes) {
+            const bool lo = lane < half_lanes;
+            const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
+            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
+                      : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
           }
         }
       }
-      uint32_t w[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) w[i] = pack_h2(x[2 * i] * p.qscale, x[2 * i + 1] * p.qscale);
-      tmem_st32(lane_addr + kTmemQ + 32 * (2 * pass + half_id), w);
-      asm volatile("bar.sync 2, 256;" ::: "memory");   // staging free for the next pass
+      const uint32_t w0 = pack_h2(v[0] * p.qscale, v[1] * p.qscale);
+      const uint32_t w1 = pack_h2(v[2] * p.qscale, v[3] * p.qscale);
+      const uint32_t w2 = pack_h2(v[4] * p.qscale, v[5] * p.qscale);
+      const uint32_t w3 = pack_h2(v[6] * p.qscale, v[7] * p.qscale);
+      // lane = 16-byte chunk of the row: sub-tile lane/8, chunk lane%8, swizzled by the row
+      const uint32_t dst = sQ + (lane >> 3) * (kPfM * 128) + r * 128 + (((lane & 7) ^ (r & 7)) << 4);
+      sts128(dst, w0, w1, w2, w3);
     }
-    tmem_wait_st();
-    tc_fence_before();
+    fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
     __syncwarp();
-    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // the MMA warp waits for all 8 warps; TMA already runs
+    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // S MMAs and V loads wait for all 8 warps
   }
 
   float l_run = 0.f;                 // softmax threads: row sum
   float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
 
-  if (warp == 8 || warp == 10) {
-    // =============================== TMA producers =================================
-    // warp 8 feeds the K ring, warp 10 the V ring. They are separate warps on purpose:
-    // two lanes of one warp waiting on different barriers hold each other up (a lane
-    // parked in try_wait parks the warp).
+  if (warp == 8) {
+    // =============================== K producer ====================================
+    // chunk g = 4 j + c: keys of tile j, dims [64 c, 64 c + 64), into slot g % 6
     if (lane == 0) {
-      const bool is_k = warp == 8;
-      const CUtensorMap *tm = is_k ? &p.tm_k : &p.tm_v;
-      const int b_full = is_k ? kBarKFull : kBarVFull, b_free = is_k ? kBarKFree : kBarVFree;
-      for (int j = 0; j < nt; ++j) {
-        const int st = j & 1;
-        if (j >= kPfStages && !mbar_wait(bars + 8 * (b_free + st), ((j >> 1) - 1) & 1, p.status, 11)) {
+      int slot = 0, use = 0;
+      for (int g = 0; g < 4 * nt; ++g) {
+        if (use > 0 && !mbar_wait(bars + 8 * (kBarKFree + slot), (use - 1) & 1, p.status, 11)) {
           s_abort = 1;
           break;
         }
         if (*(volatile int *)&s_abort) break;
-        const uint32_t full = bars + 8 * (b_full + st);
+        const uint32_t full = bars + 8 * (kBarKFull + slot);
+        if (p.debug & 32) {
+          mbar_arrive(full);
+        } else {
+          mbar_expect_tx(full, kPfKChunkBytes);
+          tma_load_2d(sK + slot * kPfKChunkBytes, &p.tm_k, kvh * kHeadDim + 64 * (g & 3), (g >> 2) * kPfN, full);
+        }
+        if (++slot == kPfKSlots) {
+          slot = 0;
+          ++use;
+        }
+      }
+    }
+  } else if (warp == 10) {
+    // =============================== V producer ====================================
+    // unit g = 2 j + u: keys [128 j + 64 u, + 64) of all 256 dims, into slot g % 2
+    if (lane == 0) {
+      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 21);  // the prologue parks a table here
+      for (int g = 0; g < 2 * nt && ok; ++g) {
+        const int slot = g & 1;
+        if (g >= 2 && !mbar_wait(bars + 8 * (kBarVFree + slot), ((g >> 1) - 1) & 1, p.status, 22)) {
+          ok = false;
+          break;
+        }
+        if (*(volatile int *)&s_abort) break;
+        const uint32_t full = bars + 8 * (kBarVFull + slot);
         if (p.debug & 32) {
           mbar_arrive(full);
           continue;
         }
-        mbar_expect_tx(full, kPfKVStageBytes / 2);
-        const uint32_t dst = sKV + st * kPfKVStageBytes + (is_k ? 0 : kPfKVStageBytes / 2);
+        mbar_expect_tx(full, kPfVUnitBytes);
 #pragma unroll
         for (int c = 0; c < 4; ++c)  // four [64 keys][64 dims] sub-tiles
-          tma_load_2d(dst + c * (kPfN * 128), tm, kvh * kHeadDim + 64 * c, j * kPfN, full);
+          tma_load_2d(sV + slot * kPfVUnitBytes + c * (kPfVUnitKeys * 128), &p.tm_v, kvh * kHeadDim + 64 * c,
+                      g * kPfVUnitKeys, full);
       }
+      if (!ok) s_abort = 1;
     }
   } else if (warp == 9) {
     // ============================ MMA issuer: S = Q K^T =============================
-    // The two contractions are issued by two threads (this one and warp 11): issuing a
-    // tcgen05.mma costs the issuing thread tens of cycles whatever its size, and with
-    // one thread the 16 small S MMAs and the 4 P V MMAs of a tile queue up behind each
-    // other's waits.
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kPfM, kPfN, false);
       // Descriptors differ only in the 16-byte-granular start address (low 14 bits, and
       // every address here is below 256 KB), so each one is a base plus a constant.
-      const uint64_t dk = smem_desc(sKV, 16, 1024);
-      RD_TR_DECL;
-      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile stored by warps 0-7
+      const uint64_t dq = smem_desc(sQ, 16, 1024);
+      const uint64_t dk = smem_desc(sK, 16, 1024);
+      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 18);  // Q tile written by warps 0-3
       tc_fence_after();
+      int slot = 0, use = 0;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
-        RD_TR(0);
-        if (!mbar_wait(bars + 8 * (kBarKFull + st), (j >> 1) & 1, p.status, 12)) { ok = false; break; }
-        RD_TR(4);
         // score buffer st still holds P(j-2) until P V of tile j-2 has read it
-        if (j >= 2 && !mbar_wait(bars + 8 * (kBarVFree + st), ((j - 2) >> 1) & 1, p.status, 15)) {
+        if (j >= 2 && !mbar_wait(bars + 8 * (kBarO + st), ((j - 2) >> 1) & 1, p.status, 15)) {
           ok = false;
           break;
         }
-        RD_TR(1);
-        tc_fence_after();
-        // S(j) into score buffer j&1: A = Q from TMEM (16 dims = 8 columns per step),
-        // B = K tile K-major, 8-row groups 1 KB apart
-        const uint64_t dks = dk + (uint64_t)((st * kPfKVStageBytes) >> 4);
-        const uint32_t d_s = tmem + kTmemS + 64 * st;
-        if (!(p.debug & 8)) {
+        const uint32_t d_s = tmem + kTmemS + 128 * st;
+        for (int c = 0; c < 4 && ok; ++c) {
+          if (!mbar_wait(bars + 8 * (kBarKFull + slot), use & 1, p.status, 12)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          // A = Q sub-tile c ([128 rows][64 dims]), B = K chunk ([128 keys][64 dims]), both
+          // K-major with 8-row groups 1 KB apart; four steps of 16 dims = 32 bytes each
+          const uint64_t a0 = dq + (uint64_t)((c * (kPfM * 128)) >> 4);
+          const uint64_t b0 = dk + (uint64_t)((slot * kPfKChunkBytes) >> 4);
+          if (!(p.debug & 8)) {
 #pragma unroll
-          for (int kk = 0; kk < 16; ++kk) {
-            const uint64_t b = dks + (uint64_t)(((kk >> 2) * (kPfN * 128) + (kk & 3) * 32) >> 4);
-            tc_mma_f16_ts(d_s, tmem + kTmemQ + 8 * kk, b, idesc_s, kk > 0);
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma_f16(d_s, a0 + (uint64_t)(2 * kk), b0 + (uint64_t)(2 * kk), idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bars + 8 * (kBarKFree + slot));  // the chunk can be refilled
+          if (++slot == kPfKSlots) {
+            slot = 0;
+            ++use;
           }
         }
-        RD_TR(5);
         tc_commit(bars + 8 * (kBarS + st));
-        tc_commit(bars + 8 * (kBarKFree + st));  // the K stage can be refilled
-        RD_TR(6);
       }
-      RD_TR_OUT(16, 7);
       if (!ok) s_abort = 1;
     }
   } else if (warp == 11) {
     // ============================ MMA issuer: O += P V ==============================
     if (lane == 0) {
       constexpr uint32_t idesc_o = idesc_f16(kPfM, kHeadDim, true);
-      const uint64_t dv = smem_desc(sKV + kPfKVStageBytes / 2, kPfN * 128, 1024);
+      const uint64_t dv = smem_desc(sV, kPfVUnitKeys * 128, 1024);
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13) ||
-            !mbar_wait(bars + 8 * (kBarVFull + st), (j >> 1) & 1, p.status, 19)) {
+        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) {
           ok = false;
           break;
         }
-        tc_fence_after();
-        // A = P(j) from TMEM (16 keys = 8 columns per step), B = V MN-major: 64-dim groups
-        // 8 KB apart (LBO), 8-key groups 1 KB apart (SBO); 4 steps of 16 keys = 2 KB each
-        const uint64_t dvs = dv + (uint64_t)((st * kPfKVStageBytes) >> 4);
-        const uint32_t a_p = tmem + kTmemS + 64 * st;
-        if (!(p.debug & 4)) {
+        for (int u = 0; u < 2 && ok; ++u) {
+          const int g = 2 * j + u, slot = g & 1;
+          if (!mbar_wait(bars + 8 * (kBarVFull + slot), (g >> 1) & 1, p.status, 19)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          // A = P(j) from TMEM (16 keys = 8 columns per step), B = V unit MN-major: 64-dim
+          // groups 8 KB apart (LBO), 8-key groups 1 KB apart (SBO); 4 steps of 16 keys
+          const uint64_t dvs = dv + (uint64_t)((slot * kPfVUnitBytes) >> 4);
+          const uint32_t a_p = tmem + kTmemS + 128 * st + 32 * u;
+          if (!(p.debug & 4)) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_f16_ts(tmem + kTmemO, a_p + 8 * kk, dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
-                          (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma_f16_ts(tmem + kTmemO, a_p + 8 * kk, dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                            (j > 0 || u > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bars + 8 * (kBarVFree + slot));  // the V unit can be refilled
         }
-        tc_commit(bars + 8 * (kBarVFree + st));  // V stage and score buffer reusable, O settled
+        tc_commit(bars + 8 * (kBarO + st));  // score buffer reusable, O settled
       }
       if (!ok) s_abort = 1;
     }
   } else {
-    // ================== softmax: thread = (row r, 32-column half ch) ==================
+    // ================== softmax: thread = (row r, 64-column half ch) ==================
     const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
-    RD_TR_DECL;
     for (int j = 0; j < nt && ok; ++j) {
       const int st = j & 1;
       if (!mbar_wait(bars + 8 * (kBarS + st), (j >> 1) & 1, p.status, 14)) { ok = false; break; }
-      RD_TR(0);
       tc_fence_after();
-      uint32_t sraw[32];
-      tmem_ld32(lane_addr + kTmemS + 64 * st + 32 * ch, sraw);
+      uint32_t s0[32], s1[32];
+      const uint32_t scol = lane_addr + kTmemS + 128 * st + 64 * ch;
+      tmem_ld32(scol, s0);
+      tmem_ld32(scol + 32, s1);
       tmem_wait_ld();
-      RD_TR(1);
-      const int key0 = j * kPfN + 32 * ch;
+      const int key0 = j * kPfN + 64 * ch;
       // only tiles that reach past some row's last key need the causal mask
-      if (__any_sync(0xffffffffu, key0 + 31 > my_pos)) {
+      if (__any_sync(0xffffffffu, key0 + 63 > my_pos)) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (key0 + i > my_pos) sraw[i] = 0xff800000u;  // -inf
+        for (int i = 0; i < 32; ++i) {
+          if (key0 + i > my_pos) s0[i] = 0xff800000u;  // -inf
+          if (key0 + 32 + i > my_pos) s1[i] = 0xff800000u;
+        }
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[i]));
+      for (int i = 0; i < 32; ++i)
+        mx[i & 3] = fmaxf(mx[i & 3], fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
       float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       s_mx[st][ch][r] = mt;
-      RD_TR(2);
       // exchange through an mbarrier (bounded wait) rather than bar.sync: a thread that
-      // gave up on a wait must not leave the others parked on a hardware barrier
-      // (this exchange also orders both halves' score loads before either half
-      // overwrites the buffer with P)
+      // gave up on a wait must not leave the others parked on a hardware barrier. (The
+      // exchange also orders both halves' score loads before either half overwrites the
+      // buffer with P.)
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarX + st));
       if (!mbar_wait(bars + 8 * (kBarX + st), (j >> 1) & 1, p.status, 20)) { ok = false; break; }
       mt = fmaxf(mt, s_mx[st][ch ^ 1][r]);   // both halves now agree on the row maximum
-      RD_TR(3);
-      RD_TR(4);
       const bool grow = mt > m_ref + kLazyThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mt);
@@ -466,7 +490,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         m_ref = m_new;
         l_run *= f;
         if (j > 0) {  // O holds data only after the first P V; and P V of tile j-1 must be done
-          if (!mbar_wait(bars + 8 * (kBarVFree + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
+          if (!mbar_wait(bars + 8 * (kBarO + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
             ok = false;
             break;
           }
@@ -484,34 +508,34 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           tmem_wait_st();
         }
       }
-      RD_TR(5);
-      // P = 2^(s - m_ref) as f16 pairs, written over the score buffer: keys 32ch..32ch+31
-      // of row r become columns 16ch..16ch+15 (the A operand of P V, read from TMEM)
+      // P = 2^(s - m_ref) as f16 pairs, written over the score buffer: keys 64ch..64ch+63
+      // of row r become columns 32ch..32ch+31 (the A operand of P V, read from TMEM)
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pw[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = (p.debug & 1) ? __uint_as_float(sraw[2 * i]) : ex2(__uint_as_float(sraw[2 * i]) - m_ref);
-        const float p1 = (p.debug & 1) ? __uint_as_float(sraw[2 * i + 1]) : ex2(__uint_as_float(sraw[2 * i + 1]) - m_ref);
+        const float p0 = (p.debug & 1) ? __uint_as_float(s0[2 * i]) : ex2(__uint_as_float(s0[2 * i]) - m_ref);
+        const float p1 = (p.debug & 1) ? __uint_as_float(s0[2 * i + 1]) : ex2(__uint_as_float(s0[2 * i + 1]) - m_ref);
         ls[i & 3] += p0 + p1;
         pw[i] = pack_h2(p0, p1);
       }
-      tmem_st16(lane_addr + kTmemS + 64 * st + 16 * ch, pw);
+      const uint32_t pcol = lane_addr + kTmemS + 128 * st + 32 * ch;
+      tmem_st16(pcol, pw);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = (p.debug & 1) ? __uint_as_float(s1[2 * i]) : ex2(__uint_as_float(s1[2 * i]) - m_ref);
+        const float p1 = (p.debug & 1) ? __uint_as_float(s1[2 * i + 1]) : ex2(__uint_as_float(s1[2 * i + 1]) - m_ref);
+        ls[i & 3] += p0 + p1;
+        pw[i] = pack_h2(p0, p1);
+      }
+      tmem_st16(pcol + 16, pw);
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      RD_TR(6);
       tmem_wait_st();
       tc_fence_before();
-      RD_TR(7);
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarP + st));
-      RD_TR(8);
     }
-#ifdef RD_PREFILL_TRACE
-    if (threadIdx.x == 0) RD_TR_OUT(0, 9);
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) g_pf_trace[15] = (unsigned long long)nt;
-#endif
-    if (ok && nt > 0 &&
-        !mbar_wait(bars + 8 * (kBarVFree + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
+    if (ok && nt > 0 && !mbar_wait(bars + 8 * (kBarO + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
       ok = false;
     if (!ok) s_abort = 1;
     tc_fence_after();
@@ -592,7 +616,7 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   memset(&a, 0, sizeof(a));
   int rc = encode_f16_tmap(&a.tm_k, k, n_head_kv, keys_total, kPfN);
   if (rc != RD_OK) return rc;
-  rc = encode_f16_tmap(&a.tm_v, v, n_head_kv, keys_total, kPfN);
+  rc = encode_f16_tmap(&a.tm_v, v, n_head_kv, keys_total, kPfVUnitKeys);
   if (rc != RD_OK) return rc;
   a.q = q;
   a.out = out;
@@ -625,9 +649,3 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
 }
 
 }  // namespace rd
-
-#ifdef RD_PREFILL_TRACE
-extern "C" int rd_prefill_trace(unsigned long long *out32) {
-  return cudaMemcpyFromSymbol(out32, rd::g_pf_trace, sizeof(rd::g_pf_trace)) == cudaSuccess ? 0 : -6;
-}
-#endif
