@@ -374,7 +374,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--leg", default="all", choices=["all", "prefill"], help=argparse.SUPPRESS)
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"], help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -606,7 +606,7 @@ def main():
     # dram__bytes_read + dram__bytes_write of one full-size launch (131001 keys), from the
     # ncu capture summarised in profiles/decode_kernel_q4_0_131001keys.md; a context slice
     # moves proportionally fewer bytes.
-    traffic = (150.99e6 + 6.83e6) * slice_rows / N_KEYS
+    traffic = (151.00e6 + 7.82e6) * slice_rows / N_KEYS
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "decode_kernel<q4_0,q4_0>", "kernel_us": k_ms * 1e3,
                 "peak_source": peak_src, "frac_of_8tbs_nominal": achieved / 8000.0}
@@ -622,15 +622,16 @@ def main():
         "us_per_layer": ms_dev / K / n_layers * 1e3,
     }
     out["config"]["exchange"] = exchange
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.leg == "all":
         out["prefill"] = prefill_leg(rd, torch, peaks)
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.leg == "all":
         refk = reference_kernel_leg(rd, torch, q_dev, N_KEYS)
         if refk is not None:
             out["reference_kernels_on_this_gpu"] = refk
-    batched = batched_leg(rd, torch, dist, rank, world, peak)
-    if rank == 0:
-        out["batched_decode"] = batched
+    if args.leg == "all":
+        batched = batched_leg(rd, torch, dist, rank, world, peak)
+        if rank == 0:
+            out["batched_decode"] = batched
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle.oracle import Oracle
         ora = Oracle()
