@@ -199,6 +199,19 @@ def prefill_leg(rd, torch, peaks):
     return res
 
 
+def deal_sequences(lens, world):
+    """Sequence sharding of the batched decode: longest first, each to the least loaded rank
+    (ties to the lowest rank). Returns one list of sequence indices per rank; every rank
+    computes the same table from the same lengths, so nothing is communicated."""
+    load = [0] * world
+    mine = [[] for _ in range(world)]
+    for i in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
+        r = min(range(world), key=lambda r: (load[r], r))
+        load[r] += lens[i]
+        mine[r].append(i)
+    return mine
+
+
 def batched_leg(rd, torch, dist, rank, world, peak):
     """Secondary measurement: BASELINE config 5 -- 64 sequences, context lengths uniform in
     [1024, 32768] from seed 7, K q8_0 / V f16, q_len 1 (decode) and 4 (verify block), all
@@ -209,13 +222,7 @@ def batched_leg(rd, torch, dist, rank, world, peak):
     import numpy as np
     L = rd.lib
     lens = [int(x) for x in np.random.default_rng(7).integers(1024, 32769, size=64)]
-    load = [0] * world
-    mine = []
-    for i in sorted(range(64), key=lambda i: -lens[i]):
-        r = min(range(world), key=lambda r: load[r])
-        load[r] += lens[i]
-        if r == rank:
-            mine.append(i)
+    mine = deal_sequences(lens, world)[rank]
     st = rd.stream_ptr()
     kcs, vcs = [], []
     for i in mine:

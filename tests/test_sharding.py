@@ -81,3 +81,23 @@ def test_two_gloo_ranks_all_gather_and_merge(tmp_path):
     out = str(tmp_path / "err.npy")
     mp.spawn(_rank_main, args=(2, port, 257, out), nprocs=2, join=True)
     assert float(np.load(out)[0]) <= 5e-6
+
+
+def test_sequence_dealing_is_a_balanced_partition():
+    """bench.py's sequence sharding (BASELINE config 5 over N GPUs): every sequence lands on
+    exactly one rank, every rank derives the same table, and the loads differ by less than
+    the longest sequence."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "bench_module", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    lens = [int(x) for x in np.random.default_rng(7).integers(1024, 32769, size=64)]
+    for world in (1, 2, 4, 8):
+        table = bench.deal_sequences(lens, world)
+        assert table == bench.deal_sequences(list(lens), world)
+        assert sorted(i for r in table for i in r) == list(range(64))
+        loads = [sum(lens[i] for i in r) for r in table]
+        assert max(loads) - min(loads) < max(lens)
+    assert bench.deal_sequences([5, 5, 5], 2) == [[0, 2], [1]]
