@@ -55,9 +55,42 @@ struct Q4Scale {
   __device__ __forceinline__ explicit Q4Scale(uint32_t d)
       : lo(hmul2(d, kH4096)), hi(hmul2(d, kH256)), c(hmul2(d, kHNeg2m9)) {}
 };
-// One word of 8 nibbles, bytes (B0,B1,B2,B3) -> four half2 of d*(n-8)*2^-12:
+// q4_1: value = d*n + m (kv.h:219-229), same trick with the block minimum as the addend:
+//   fma(n * 2^-24, d * 2^12, m * 2^-12) = (d*n + m) * 2^-12.
+// (m * 2^-12 is a subnormal half for |m| < 1/4: at most 2^-13 of absolute error in the
+// value, far inside the attention gates.)
+constexpr uint32_t kH2m12 = 0x0C000C00u;    // half2(2^-12, 2^-12)
+struct Q41Scale {
+  uint32_t lo, hi, c;
+  __device__ __forceinline__ Q41Scale(uint32_t d, uint32_t m)
+      : lo(hmul2(d, kH4096)), hi(hmul2(d, kH256)), c(hmul2(m, kH2m12)) {}
+};
+// q5_0: value = d * ((nibble | bit5 << 4) - 16) (kv.h:203-216). The fifth bits of the four
+// low-nibble and the four high-nibble elements of a word (bit i = byte i, bits above 7
+// clear) are spread to bit 4 of each byte with one multiply -- bit i * 2^(4+7j) lands on
+// 4+8j exactly for i == j and on positions the mask drops otherwise -- and OR-ed under the
+// masked nibbles; the rest is the q4_0 trick with a 5-bit mantissa field:
+//   fma(v * 2^-24, d * 2^12, -d * 2^-8) = d * (v - 16) * 2^-12.
+constexpr uint32_t kHNeg2m8 = 0x9C009C00u;  // half2(-2^-8, -2^-8)
+struct Q5Scale {
+  uint32_t m, c;
+  __device__ __forceinline__ explicit Q5Scale(uint32_t d) : m(hmul2(d, kH4096)), c(hmul2(d, kHNeg2m8)) {}
+};
 //   l0 = (B0.lo, B2.lo), h0 = (B0.hi, B2.hi), l1 = (B1.lo, B3.lo), h1 = (B1.hi, B3.hi)
-__device__ __forceinline__ void dq4(uint32_t x, const Q4Scale &s, uint32_t &l0, uint32_t &h0,
+__device__ __forceinline__ void dq5(uint32_t x, uint32_t bl, uint32_t bh, const Q5Scale &s, uint32_t &l0,
+                                    uint32_t &h0, uint32_t &l1, uint32_t &h1) {
+  const uint32_t xl = (x & 0x0F0F0F0Fu) | ((bl * 0x02040810u) & 0x10101010u);
+  const uint32_t xh = ((x >> 4) & 0x0F0F0F0Fu) | ((bh * 0x02040810u) & 0x10101010u);
+  l0 = hfma2(xl & 0x001F001Fu, s.m, s.c);
+  l1 = hfma2((xl >> 8) & 0x001F001Fu, s.m, s.c);
+  h0 = hfma2(xh & 0x001F001Fu, s.m, s.c);
+  h1 = hfma2((xh >> 8) & 0x001F001Fu, s.m, s.c);
+}
+// One word of 8 nibbles, bytes (B0,B1,B2,B3) -> four half2 of d*(n-8)*2^-12 (Q4Scale) or
+// (d*n+m)*2^-12 (Q41Scale):
+//   l0 = (B0.lo, B2.lo), h0 = (B0.hi, B2.hi), l1 = (B1.lo, B3.lo), h1 = (B1.hi, B3.hi)
+template <class Scale>
+__device__ __forceinline__ void dq4(uint32_t x, const Scale &s, uint32_t &l0, uint32_t &h0,
                                     uint32_t &l1, uint32_t &h1) {
   const uint32_t y = x >> 8;
   l0 = hfma2(x & 0x000F000Fu, s.lo, s.c);
@@ -213,62 +246,82 @@ struct KLoad<RD_KV_F32> {
   }
 };
 
-// ---- q5_0 / q4_1: element-wise loaders -------------------------------------------------
-// The reference's default 131K configuration stores K as q5_0 and V as q4_1
-// (include/rdna4/kv.h:75-98). Their 22- and 20-byte blocks are read here value by value
-// (kv_load of kv.h:208-229 restated on shared memory): correct for every K x V pair, but
-// without the word-wide unpacking tricks of the q4_0 / q8_0 loaders above.
-__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float lds_f16(uint32_t addr) {
-  unsigned short v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return __half2float(__ushort_as_half(v));
-}
-template <int T>
-__device__ __forceinline__ float dequant_elem(uint32_t row, int d);
+// ---- q5_0 / q4_1: the reference's default 131K configuration stores K as q5_0 and V as
+// q4_1 (include/rdna4/kv.h:75-98); kv_load of kv.h:203-229 restated on fragments.
 template <>
-__device__ __forceinline__ float dequant_elem<RD_KV_Q5_0>(uint32_t row, int d) {
-  const uint32_t b = row + 22u * (uint32_t)(d >> 5);
-  const int j = d & 31;
-  const uint32_t byte = lds_u8(b + 6 + (j & 15));
-  const int nib = j < 16 ? (int)(byte & 15u) : (int)(byte >> 4);
-  const int hi = (int)(lds_u8(b + 2 + (j >> 3)) >> (j & 7)) & 1;
-  return lds_f16(b) * (float)((nib | (hi << 4)) - 16);
-}
-template <>
-__device__ __forceinline__ float dequant_elem<RD_KV_Q4_1>(uint32_t row, int d) {
-  const uint32_t b = row + 20u * (uint32_t)(d >> 5);
-  const int j = d & 31;
-  const uint32_t byte = lds_u8(b + 4 + (j & 15));
-  const int q = j < 16 ? (int)(byte & 15u) : (int)(byte >> 4);
-  return __fadd_rn(__fmul_rn(lds_f16(b), (float)q), lds_f16(b + 2));
-}
-
-template <int T>
-struct KLoadElem {
-  static constexpr float kUnscale = 1.0f;
-  // the plain m16n8k16 A layout: slots (2t, 2t+1, 2t+8, 2t+9) of k-step n
-  __device__ static int dim(int t, int n, int e) { return 16 * n + 2 * t + (e & 1) + 8 * (e >> 1); }
+struct KLoad<RD_KV_Q5_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane t owns blocks 2t and 2t+1 of the row: 44 bytes at 44t = eleven aligned words.
+  // Block 2t is d | qh | 16 nibble bytes from byte 0, so its qh and nibble words straddle
+  // two loaded words (realigned with PRMT); block 2t+1 starts at byte 22: d is the upper
+  // half of word 5, qh is word 6 and the nibbles are words 7..10.
+  __device__ static int dim(int t, int n, int e) {
+    const int x = n >> 1;
+    return (2 * t + (x >> 2)) * 32 + 4 * (x & 3) + (n & 1) + ((e & 1) ? 2 : 0) + ((e & 2) ? 16 : 0);
+  }
   template <class F>
   __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+    uint32_t wg[11], wh[11];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      const int d0 = 16 * n + 2 * t;
-      mma(n, pack_h2(dequant_elem<T>(row_g, d0), dequant_elem<T>(row_g, d0 + 1)),
-          pack_h2(dequant_elem<T>(row_h, d0), dequant_elem<T>(row_h, d0 + 1)),
-          pack_h2(dequant_elem<T>(row_g, d0 + 8), dequant_elem<T>(row_g, d0 + 9)),
-          pack_h2(dequant_elem<T>(row_h, d0 + 8), dequant_elem<T>(row_h, d0 + 9)));
+    for (int i = 0; i < 11; ++i) {
+      wg[i] = lds32(row_g + 44 * t + 4 * i);
+      wh[i] = lds32(row_h + 44 * t + 4 * i);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const Q5Scale sg(b == 0 ? prmt(wg[0], wg[0], 0x1010u) : prmt(wg[5], wg[5], 0x3232u));
+      const Q5Scale sh(b == 0 ? prmt(wh[0], wh[0], 0x1010u) : prmt(wh[5], wh[5], 0x3232u));
+      const uint32_t qhg = b == 0 ? prmt(wg[0], wg[1], 0x5432u) : wg[6];
+      const uint32_t qhh = b == 0 ? prmt(wh[0], wh[1], 0x5432u) : wh[6];
+#pragma unroll
+      for (int xx = 0; xx < 4; ++xx) {
+        const int x = 4 * b + xx;
+        const uint32_t xg = b == 0 ? prmt(wg[1 + xx], wg[2 + xx], 0x5432u) : wg[7 + xx];
+        const uint32_t xh = b == 0 ? prmt(wh[1 + xx], wh[2 + xx], 0x5432u) : wh[7 + xx];
+        uint32_t l0g, h0g, l1g, h1g, l0h, h0h, l1h, h1h;
+        dq5(xg, (qhg >> (4 * xx)) & 0xFu, (qhg >> (16 + 4 * xx)) & 0xFu, sg, l0g, h0g, l1g, h1g);
+        dq5(xh, (qhh >> (4 * xx)) & 0xFu, (qhh >> (16 + 4 * xx)) & 0xFu, sh, l0h, h0h, l1h, h1h);
+        mma(2 * x, l0g, l0h, h0g, h0h);
+        mma(2 * x + 1, l1g, l1h, h1g, h1h);
+      }
     }
   }
 };
 template <>
-struct KLoad<RD_KV_Q5_0> : KLoadElem<RD_KV_Q5_0> {};
-template <>
-struct KLoad<RD_KV_Q4_1> : KLoadElem<RD_KV_Q4_1> {};
+struct KLoad<RD_KV_Q4_1> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane t owns blocks t and t+4 of the row: five aligned words each ((d, m), then four
+  // words of nibbles) at 20t and 20t + 80. (Blocks 2t and 2t+1 would put the four lanes
+  // of a row 10 words apart: with the row pitch of 4 words mod 32 that is a 2-way bank
+  // conflict on every load; 5 words apart is conflict-free.)
+  __device__ static int dim(int t, int n, int e) {
+    const int x = n >> 1;
+    return (t + 4 * (x >> 2)) * 32 + 4 * (x & 3) + (n & 1) + ((e & 1) ? 2 : 0) + ((e & 2) ? 16 : 0);
+  }
+  template <class F>
+  __device__ static void run(uint32_t row_g, uint32_t row_h, int t, F &&mma) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {   // one block at a time: ten words live, not twenty
+      uint32_t wg[5], wh[5];
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        wg[i] = lds32(row_g + 20 * t + 80 * b + 4 * i);
+        wh[i] = lds32(row_h + 20 * t + 80 * b + 4 * i);
+      }
+      const Q41Scale sg(prmt(wg[0], wg[0], 0x1010u), prmt(wg[0], wg[0], 0x3232u));
+      const Q41Scale sh(prmt(wh[0], wh[0], 0x1010u), prmt(wh[0], wh[0], 0x3232u));
+#pragma unroll
+      for (int xx = 0; xx < 4; ++xx) {
+        const int x = 4 * b + xx;
+        uint32_t l0g, h0g, l1g, h1g, l0h, h0h, l1h, h1h;
+        dq4(wg[1 + xx], sg, l0g, h0g, l1g, h1g);
+        dq4(wh[1 + xx], sh, l0h, h0h, l1h, h1h);
+        mma(2 * x, l0g, l0h, h0g, h0h);
+        mma(2 * x + 1, l1g, l1h, h1g, h1h);
+      }
+    }
+  }
+};
 
 // =============================== V loaders =======================================
 // A fragment of V^T*P for M-tile m (0..15): rows g / g+8 = two true dims chosen by
@@ -408,27 +461,80 @@ struct VLoad<RD_KV_F32> {
   }
 };
 
-template <int T>
-struct VLoadElem {
-  static constexpr float kUnscale = 1.0f;
-  // the plain A layout of V^T: rows g / g+8 of M-tile m are dims 16m+g / 16m+g+8
-  __device__ static int dim(int g, int m, int r) { return 16 * m + g + 8 * r; }
+template <>
+struct VLoad<RD_KV_Q5_0> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane g owns block g of each key: 22 bytes at 22g, read as six aligned words from
+  // (22g & ~3); for odd g the block starts in the upper half of the first word, which
+  // shifts d, qh and the nibble words by two bytes (one PRMT selector per case).
+  __device__ static int dim(int g, int m, int r) { return 32 * g + m + 16 * r; }
   template <class F>
   __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+    const uint32_t off = (22u * g) & ~3u;
+    const bool par = g & 1;
+    const uint32_t sel = par ? 0x7654u : 0x5432u;   // odd g: the next word is already aligned
+    uint32_t dd[4], qh[4], qs[4][4];
 #pragma unroll
-    for (int m = 0; m < 16; ++m) {
-      const int d0 = 16 * m + g, d1 = d0 + 8;
-      mma(m, pack_h2(dequant_elem<T>(rows[0], d0), dequant_elem<T>(rows[1], d0)),
-          pack_h2(dequant_elem<T>(rows[0], d1), dequant_elem<T>(rows[1], d1)),
-          pack_h2(dequant_elem<T>(rows[2], d0), dequant_elem<T>(rows[3], d0)),
-          pack_h2(dequant_elem<T>(rows[2], d1), dequant_elem<T>(rows[3], d1)));
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w[6];
+#pragma unroll
+      for (int i = 0; i < 6; ++i) w[i] = lds32(rows[j] + off + 4 * i);
+      dd[j] = prmt(w[0], w[0], par ? 0x3232u : 0x1010u);
+      qh[j] = prmt(w[0], w[1], sel);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) qs[j][x] = prmt(w[1 + x], w[2 + x], sel);
+    }
+    const Q5Scale sab(prmt(dd[0], dd[1], 0x5410u)), scd(prmt(dd[2], dd[3], 0x5410u));
+    // fifth bits of element pairs, two keys side by side: nibble (s & ~1) * 2 of pe (even
+    // slots s) / po (odd slots) holds (key0 bits 2s, 2s+1 | key1 bits 2s, 2s+1)
+    const uint32_t pe_ab = (qh[0] & 0x33333333u) | ((qh[1] & 0x33333333u) << 2);
+    const uint32_t po_ab = ((qh[0] >> 2) & 0x33333333u) | (qh[1] & 0xCCCCCCCCu);
+    const uint32_t pe_cd = (qh[2] & 0x33333333u) | ((qh[3] & 0x33333333u) << 2);
+    const uint32_t po_cd = ((qh[2] >> 2) & 0x33333333u) | (qh[3] & 0xCCCCCCCCu);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {   // bytes 2s, 2s+1 of the nibbles: elements 2s, 2s+1 (+16)
+      const uint32_t psel = (s & 1) ? 0x7632u : 0x5410u;
+      const uint32_t xab = prmt(qs[0][s >> 1], qs[1][s >> 1], psel);
+      const uint32_t xcd = prmt(qs[2][s >> 1], qs[3][s >> 1], psel);
+      const int sh = 4 * (s >> 1);
+      const uint32_t bab = (s & 1) ? po_ab : pe_ab, bcd = (s & 1) ? po_cd : pe_cd;
+      uint32_t l0a, h0a, l1a, h1a, l0c, h0c, l1c, h1c;
+      dq5(xab, (bab >> sh) & 0xFu, (bab >> (16 + sh)) & 0xFu, sab, l0a, h0a, l1a, h1a);
+      dq5(xcd, (bcd >> sh) & 0xFu, (bcd >> (16 + sh)) & 0xFu, scd, l0c, h0c, l1c, h1c);
+      mma(2 * s, l0a, h0a, l0c, h0c);
+      mma(2 * s + 1, l1a, h1a, l1c, h1c);
     }
   }
 };
 template <>
-struct VLoad<RD_KV_Q5_0> : VLoadElem<RD_KV_Q5_0> {};
-template <>
-struct VLoad<RD_KV_Q4_1> : VLoadElem<RD_KV_Q4_1> {};
+struct VLoad<RD_KV_Q4_1> {
+  static constexpr float kUnscale = kQuantUnscale;
+  // lane g owns block g of each key: 20 bytes at 20g = five aligned words.
+  __device__ static int dim(int g, int m, int r) { return 32 * g + m + 16 * r; }
+  template <class F>
+  __device__ static void run(const uint32_t (&rows)[4], int g, F &&mma) {
+    uint32_t w[4][5];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 5; ++i) w[j][i] = lds32(rows[j] + 20u * g + 4 * i);
+    // half2 across two keys: (key a, key b) and (key c, key d), each with its own (d, m)
+    const Q41Scale sab(prmt(w[0][0], w[1][0], 0x5410u), prmt(w[0][0], w[1][0], 0x7632u));
+    const Q41Scale scd(prmt(w[2][0], w[3][0], 0x5410u), prmt(w[2][0], w[3][0], 0x7632u));
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {   // bytes 2s, 2s+1 of the nibbles: elements 2s, 2s+1 (+16)
+      const int i = 1 + (s >> 1);
+      const uint32_t sel = (s & 1) ? 0x7632u : 0x5410u;
+      const uint32_t xab = prmt(w[0][i], w[1][i], sel);
+      const uint32_t xcd = prmt(w[2][i], w[3][i], sel);
+      uint32_t l0a, h0a, l1a, h1a, l0c, h0c, l1c, h1c;
+      dq4(xab, sab, l0a, h0a, l1a, h1a);
+      dq4(xcd, scd, l0c, h0c, l1c, h1c);
+      mma(2 * s, l0a, h0a, l0c, h0c);
+      mma(2 * s + 1, l1a, h1a, l1c, h1c);
+    }
+  }
+};
 
 // =============================== kernel ==========================================
 struct DecodeKernelArgs {
