@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload at every N: BASELINE config 4 -- long-context decode, 1 sequence, q_len 1,
+Workload at every N: benchmark config 4 -- long-context decode, 1 sequence, q_len 1,
 24 query / 4 KV heads, head_dim 256, the token at position 131000 attends 131001 keys
 of a q4_0/q4_0 cache. One STEP is that token's attention in the engine's 16
 full-attention layers, each with its own K/V cache: per layer the new K/V row is
@@ -138,7 +138,7 @@ def reference_arm(args):
 
 def prefill_leg(rd, torch, peaks):
     """Secondary measurement (1 GPU): the causal prefill kernel on the tensor roofline.
-    BASELINE config 3 -- 512 new tokens at position 0, f16 K/V, one layer: K/V append with
+    benchmark config 3 -- 512 new tokens at position 0, f16 K/V, one layer: K/V append with
     the K RoPE fused, then prefill attention with the Q RoPE and the sigmoid gate fused --
     and the reference's own FA2 admission window (512 queries over 2048..8192 keys).
     TFLOP/s counts causal-useful flops 4*256*24*sum(pos+1); peak = measured bf16 burst."""
@@ -213,7 +213,7 @@ def deal_sequences(lens, world):
 
 
 def batched_leg(rd, torch, dist, rank, world, peak):
-    """Secondary measurement: BASELINE config 5 -- 64 sequences, context lengths uniform in
+    """Secondary measurement: benchmark config 5 -- 64 sequences, context lengths uniform in
     [1024, 32768] from seed 7, K q8_0 / V f16, q_len 1 (decode) and 4 (verify block), all
     sequences of a rank in ONE rd_attn_decode_multi call. With N GPUs the sequences are
     dealt out greedily by length (longest first to the least loaded rank); there is no

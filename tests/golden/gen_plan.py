@@ -1,5 +1,5 @@
 """Writes b200_plan.txt: the decode plan of the library (tile keys, TMA ring stages, internal
-split count) for every K x V type pair at the BASELINE context lengths on a 148-SM B200,
+split count) for every K x V type pair at the benchmark context lengths on a 148-SM B200,
 and the reference's caller-side split rule for the same shapes. Needs only the built
 library (host arithmetic, no GPU):
 

@@ -1,4 +1,4 @@
-"""BASELINE configs 1 and 2 as named parity cases (config 3 is test_gpu_prefill.py::
+"""benchmark configs 1 and 2 as named parity cases (config 3 is test_gpu_prefill.py::
 test_prefill_fused_rope_and_gate, config 4 test_gpu_attn.py::test_long_context_q4_0_full_size,
 config 5 test_gpu_multi.py::test_batched_decode_64_sequences). Inputs are seeded synthetic
 N(0,1) tensors of the stated shapes; gates: KV bytes as the oracle's quantizer writes them,

@@ -73,7 +73,7 @@ def test_prefill_ragged_positions_and_empty_rows(G, oracle, rd):
 
 
 def test_prefill_fused_rope_and_gate(G, oracle, rd):
-    """BASELINE config 3 in one piece: 512 tokens at position 0, K/V appended as f16 with the
+    """benchmark config 3 in one piece: 512 tokens at position 0, K/V appended as f16 with the
     K RoPE fused into the append, Q RoPE and the sigmoid gate fused into the prefill."""
     import torch
     rng = np.random.default_rng(0)

@@ -84,7 +84,7 @@ def test_two_gloo_ranks_all_gather_and_merge(tmp_path):
 
 
 def test_sequence_dealing_is_a_balanced_partition():
-    """bench.py's sequence sharding (BASELINE config 5 over N GPUs): every sequence lands on
+    """bench.py's sequence sharding (benchmark config 5 over N GPUs): every sequence lands on
     exactly one rank, every rank derives the same table, and the loads differ by less than
     the longest sequence."""
     import importlib.util
