@@ -177,6 +177,20 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
                       int k_type, int v_type, int n_splits, float *gate, void *workspace,
                       size_t workspace_bytes, void *stream);
 
+/* ---- append + decode in two launches (no counterpart: the reference runs
+ * kv_store_row_launch twice, then attn_launch_split, graph.cuh:1011-1035 and 958-977).
+ * Stores k_new / v_new ([n_head_kv][head_dim] f32, K already normalised and rotated) as
+ * row t of the caches and returns the attention of q over keys 0..t, the new one
+ * included: the first CTAs of the split-KV launch quantize and store the row while the
+ * launch attends keys 0..t-1, and the merge folds key t in from the cache. Cache bytes
+ * equal rd_kv_append's; the output equals rd_attn_decode_ws after rd_kv_append within
+ * the attention tolerance. q must not alias out (RD_ERR_UNSUPPORTED). gate as in
+ * rd_attn_decode_ws; workspace from rd_attn_workspace_bytes(1, ...). */
+int rd_attn_decode_append_ws(const float *q, const float *k_new, const float *v_new, void *k_cache,
+                             void *v_cache, float *out, int t, int n_head, int n_head_kv, int head_dim,
+                             float scale, int k_type, int v_type, float *gate, void *workspace,
+                             size_t workspace_bytes, void *stream);
+
 /* ---- many sequences in one launch (decode and short verify blocks).
  *
  * The reference serves one sequence per Graph (graph.cuh:958-977 decode,

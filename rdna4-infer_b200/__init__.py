@@ -50,6 +50,8 @@ SIGNATURES = {
     "rd_attn_decode_split": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P]),
     "rd_attn_decode_ws": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                C.c_size_t, _P]),
+    "rd_attn_decode_append_ws": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, C.c_size_t,
+                                      _P]),
     "rd_attn_multi_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I]),
     "rd_attn_decode_multi": (_I, [_P, _I, _I, _I, _I, _I, _F, _I, _I, _P, C.c_size_t, _P]),
     "rd_shard_xbuf_bytes": (C.c_size_t, [_I, _I, _I]),

@@ -437,6 +437,59 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
                    sm_count(dev), (cudaStream_t)stream);
 }
 
+int rd_attn_decode_append_ws(const float *q, const float *k_new, const float *v_new, void *k_cache,
+                             void *v_cache, float *out, int t, int n_head, int n_head_kv, int head_dim,
+                             float scale, int k_type, int v_type, float *gate, void *workspace,
+                             size_t workspace_bytes, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (t < 0) return RD_ERR_SHAPE;
+  if (q == nullptr || k_new == nullptr || v_new == nullptr || k_cache == nullptr ||
+      v_cache == nullptr || out == nullptr)
+    return RD_ERR_NULL;
+  if (q == out) return RD_ERR_UNSUPPORTED;  // the merge reads whole query rows while it writes out
+  if (workspace == nullptr) return RD_ERR_WORKSPACE;
+  if (!aligned(q, 4) || !aligned(out, 4) || !aligned(gate, 4) || !aligned(k_new, 4) || !aligned(v_new, 4))
+    return RD_ERR_ALIGN;
+  if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
+  int dev;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  // keys 0..t-1 through the split-KV kernel (whose first CTAs also store row t), then the
+  // merge with row t folded in
+  const int tile = decode_tile_keys(k_type, v_type);
+  const int64_t tiles = ((int64_t)t + tile - 1) / tile;
+  const int S = plan_splits(sm_count(dev), 1, tiles);
+  if (workspace_bytes < partial_floats(1, n_head, S) * sizeof(float)) return RD_ERR_WORKSPACE;
+  DecodeArgs a;
+  a.q = q;
+  a.k = k_cache;
+  a.v = v_cache;
+  a.partial = (float *)workspace;
+  a.pos = nullptr;
+  a.t = t - 1;
+  a.key_begin = 0;
+  a.n_tok = 1;
+  a.n_head = n_head;
+  a.n_head_kv = n_head_kv;
+  a.scale = scale;
+  a.n_splits = S;
+  a.status = status_word(dev, false);
+  a.k_new = k_new;
+  a.v_new = v_new;
+  a.new_row = t;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = launch_decode(k_type, v_type, a, st)) != RD_OK) return rc;
+  ExtraKey x;
+  x.q = q;
+  x.k_row = (const uint8_t *)k_cache + (size_t)t * n_head_kv * row_bytes(k_type);
+  x.v_row = (const uint8_t *)v_cache + (size_t)t * n_head_kv * row_bytes(v_type);
+  x.kt = k_type;
+  x.vt = v_type;
+  x.nkv = n_head_kv;
+  x.scale = scale;
+  return launch_merge_extra((const float *)workspace, out, n_head, S, gate, x, st);
+}
+
 int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *out, int t,
                            int n_head, int n_head_kv, int head_dim, float scale, int k_type,
                            int v_type, float *gate, void *stream) {

@@ -40,6 +40,7 @@
 #include <type_traits>
 
 #include "rd_internal.h"
+#include "rd_quant.cuh"
 
 namespace rd {
 
@@ -563,6 +564,11 @@ struct DecodeKernelArgs {
   const DecodeSeq *seqs;
   const int4 *items;
   int q_len;
+  // Fused append (single-sequence launches): quantize k_new / v_new [nkv][256] into cache
+  // row new_row; null = nothing to append.
+  const float *k_new;
+  const float *v_new;
+  int new_row;
 };
 
 template <int KT, int VT, bool MULTI>
@@ -651,6 +657,23 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const int key0 = key_begin + tile_b * TILE;
 
   __syncthreads();
+  // Fused append: the newest position's K and V rows are quantized by the consumer warps
+  // of the first CTAs (one 32-value block per warp) while the first tiles are in flight.
+  // Nobody in this launch reads that row: the keys attended end before it, and the merge
+  // that follows folds it in from the cache.
+  if constexpr (!MULTI) {
+    if (p.k_new != nullptr && warp < CW && blockIdx.y == 0) {
+      const int per_tensor = nkv * (kHeadDim / 32);
+      for (int b = (int)blockIdx.x * CW + warp; b < 2 * per_tensor; b += (int)gridDim.x * CW) {
+        if (b < per_tensor)
+          store_block<KT>(p.k_new[b * 32 + lane], const_cast<uint8_t *>(p.k) + (size_t)p.new_row * nkv * RK, b,
+                          lane);
+        else
+          store_block<VT>(p.v_new[(b - per_tensor) * 32 + lane],
+                          const_cast<uint8_t *>(p.v) + (size_t)p.new_row * nkv * RV, b - per_tensor, lane);
+      }
+    }
+  }
   // Query fragments. Lane (g, tq) of every consumer warp of a kv head needs the same 32
   // words: head g's values at the dims KL::dim(tq, n, 0..3), n = 0..15, as f16 pairs
   // pre-scaled into log2 units (and by the loader's fixed-point factor). The consumer
@@ -1073,6 +1096,9 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.stages = stages;
   k.debug = decode_debug_mask();
   k.status = a.status;
+  k.k_new = a.k_new;
+  k.v_new = a.v_new;
+  k.new_row = a.new_row;
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
   return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3((4 * KG + 1) * 32), smem, st, k) ==
                  cudaSuccess

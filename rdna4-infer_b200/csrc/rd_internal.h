@@ -48,6 +48,12 @@ struct DecodeArgs {
   float scale;
   int n_splits;
   DeviceStatus *status;
+  // Fused append (optional, single token only): the f32 rows k_new / v_new
+  // [n_head_kv][256] are quantized and stored as cache row `new_row` by the first CTAs of
+  // the launch; the keys attended are still key_begin..t (pass t = new_row - 1).
+  const float *k_new = nullptr;
+  const float *v_new = nullptr;
+  int new_row = 0;
 };
 int launch_decode(int kt, int vt, const DecodeArgs &a, cudaStream_t st);
 
@@ -117,6 +123,19 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
 // partial [n_rows][n_splits][258] -> out [n_rows][256]; optional fused sigmoid gate.
 int launch_merge(const float *partial, float *out, int n_rows, int n_splits, float *gate,
                  cudaStream_t st);
+// The same merge with one more key folded in: the key stored at k_row / v_row (cache row
+// of the newest position, types kt / vt, n_head_kv heads) attended by q [n_rows][256]
+// with `scale`, as if it were one more record (m = score, l = 1, acc = v). q must not
+// alias out.
+struct ExtraKey {
+  const float *q;
+  const uint8_t *k_row;
+  const uint8_t *v_row;
+  int kt, vt, nkv;
+  float scale;
+};
+int launch_merge_extra(const float *partial, float *out, int n_rows, int n_splits, float *gate,
+                       const ExtraKey &x, cudaStream_t st);
 // partial [n_rows][n_in][258] -> records [n_rows][n_out][258]: record j merges the
 // input records [j*n_in/n_out, (j+1)*n_in/n_out).
 int launch_merge_records(const float *partial, float *records, int n_rows, int n_in, int n_out,

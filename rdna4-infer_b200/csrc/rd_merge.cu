@@ -16,13 +16,51 @@ namespace rd {
 constexpr int kMergeDims = 64;    // dims per CTA
 constexpr int kMergeGroups = 16;  // record groups per CTA
 
+// One stored value of a cache row (kv_load, include/rdna4/kv.h:174-229), type chosen at run
+// time: used for the single newest key the merge can fold in (see MODE 3).
+__device__ __forceinline__ float load_cache_value(const uint8_t *row, int type, int d) {
+  const int b = d >> 5, j = d & 31;
+  auto h2f = [](const uint8_t *p) { return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p))); };
+  switch (type) {
+    case RD_KV_F32: return reinterpret_cast<const float *>(row)[d];
+    case RD_KV_F16: return h2f(row + 2 * d);
+    case RD_KV_Q8_0: {
+      const uint8_t *blk = row + 34 * b;
+      return __fmul_rn(h2f(blk), (float)(int8_t)blk[2 + j]);
+    }
+    case RD_KV_Q4_0: {
+      const uint8_t *blk = row + 18 * b;
+      const int byte = blk[2 + (j & 15)];
+      return __fmul_rn(h2f(blk), (float)((j < 16 ? (byte & 15) : (byte >> 4)) - 8));
+    }
+    case RD_KV_Q5_0: {
+      const uint8_t *blk = row + 22 * b;
+      const int byte = blk[6 + (j & 15)];
+      const int hi = (blk[2 + (j >> 3)] >> (j & 7)) & 1;
+      return __fmul_rn(h2f(blk), (float)(((j < 16 ? (byte & 15) : (byte >> 4)) | (hi << 4)) - 16));
+    }
+    default: {  // RD_KV_Q4_1
+      const uint8_t *blk = row + 20 * b;
+      const int byte = blk[4 + (j & 15)];
+      return __fadd_rn(__fmul_rn(h2f(blk), (float)(j < 16 ? (byte & 15) : (byte >> 4))), h2f(blk + 2));
+    }
+  }
+}
+__host__ __device__ constexpr int merge_row_bytes(int type) {
+  return type == RD_KV_F32 ? 1024 : type == RD_KV_F16 ? 512 : type == RD_KV_Q8_0 ? 272 : type == RD_KV_Q4_0 ? 144
+         : type == RD_KV_Q5_0 ? 176 : 160;
+}
+
 // MODE 0: normalised output (optionally gated). MODE 1: un-normalised record out.
+// MODE 3: like 0, plus one more key -- the newest position's row, still only in the cache
+// -- attended here as one more record (m = scale * q.k, l = 1, acc = v).
 // MODE 2: like 0, but row = (sequence, token, head) and the record block, split count,
 // output and gate come from the sequence's descriptor (rows_per_seq = q_len * n_head).
 template <int MODE>
 __global__ void __launch_bounds__(kMergeDims *kMergeGroups)
 merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_in, int n_out,
-             float *__restrict__ gate, const DecodeSeq *__restrict__ seqs, int rows_per_seq) {
+             float *__restrict__ gate, const DecodeSeq *__restrict__ seqs, int rows_per_seq,
+             const ExtraKey xk) {
   __shared__ float s_l[kMergeGroups];
   __shared__ float s_acc[kMergeGroups][kMergeDims];
   __shared__ float s_mm;
@@ -47,8 +85,29 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     hi = n_in;
   }
 
+  // MODE 3: the score of the extra key, by the first 256 threads (one dim each)
+  float x_score = -INFINITY;
+  const uint8_t *x_vrow = nullptr;
+  if (MODE == 3) {
+    __shared__ float s_dot[8];
+    const int kvh = row / kGroup;
+    float prod = 0.f;
+    if (threadIdx.x < kHeadDim)
+      prod = xk.q[(size_t)row * kHeadDim + threadIdx.x] *
+             load_cache_value(xk.k_row + (size_t)kvh * merge_row_bytes(xk.kt), xk.kt, threadIdx.x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
+    if (threadIdx.x < kHeadDim && (threadIdx.x & 31) == 0) s_dot[threadIdx.x >> 5] = prod;
+    __syncthreads();
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot += s_dot[i];
+    x_score = dot * xk.scale;
+    x_vrow = xk.v_row + (size_t)kvh * merge_row_bytes(xk.vt);
+  }
+
   // pass 1: the maximum over this output's records
-  float mx = -INFINITY;
+  float mx = MODE == 3 ? x_score : -INFINITY;
   for (int s = lo + threadIdx.x; s < hi; s += blockDim.x) mx = fmaxf(mx, base[(size_t)s * kRec]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -86,6 +145,11 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
       l += s_l[i];
     }
     const int d = quarter * kMergeDims + tx;
+    if (MODE == 3) {
+      const float w = expf(x_score - mm);
+      a = fmaf(load_cache_value(x_vrow, xk.vt, d), w, a);
+      l += w;
+    }
     if (MODE != 1) {
       float o = (mm != -INFINITY && l > 0.f) ? a / l : 0.f;
       float *op = out + (size_t)out_row * kHeadDim + d;
@@ -112,7 +176,17 @@ int launch_merge(const float *partial, float *out, int n_rows, int n_splits, flo
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, 1);
   return launch_pdl(4, merge_kernel<0>, grid, dim3(kMergeDims * kMergeGroups), 0, st, partial, out, n_splits,
-                    1, gate, nullptr, 1) == cudaSuccess
+                    1, gate, nullptr, 1, ExtraKey{}) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_CUDA;
+}
+
+int launch_merge_extra(const float *partial, float *out, int n_rows, int n_splits, float *gate,
+                       const ExtraKey &x, cudaStream_t st) {
+  if (n_rows == 0) return RD_OK;
+  const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, 1);
+  return launch_pdl(4, merge_kernel<3>, grid, dim3(kMergeDims * kMergeGroups), 0, st, partial, out, n_splits,
+                    1, gate, nullptr, 1, x) == cudaSuccess
              ? RD_OK
              : RD_ERR_CUDA;
 }
@@ -122,7 +196,7 @@ int launch_merge_records(const float *partial, float *records, int n_rows, int n
   if (n_rows == 0) return RD_OK;
   const dim3 grid((unsigned)n_rows, kHeadDim / kMergeDims, (unsigned)n_out);
   return launch_pdl(4, merge_kernel<1>, grid, dim3(kMergeDims * kMergeGroups), 0, st, partial, records, n_in,
-                    n_out, nullptr, nullptr, 1) == cudaSuccess
+                    n_out, nullptr, nullptr, 1, ExtraKey{}) == cudaSuccess
              ? RD_OK
              : RD_ERR_CUDA;
 }
@@ -133,7 +207,7 @@ int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_se
   if (rows == 0) return RD_OK;
   const dim3 grid((unsigned)rows, kHeadDim / kMergeDims, 1);
   return launch_pdl(4, merge_kernel<2>, grid, dim3(kMergeDims * kMergeGroups), 0, st, records, nullptr, 0, 1,
-                    nullptr, dev_seqs, q_len * n_head) == cudaSuccess
+                    nullptr, dev_seqs, q_len * n_head, ExtraKey{}) == cudaSuccess
              ? RD_OK
              : RD_ERR_CUDA;
 }
