@@ -642,14 +642,16 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle.oracle import Oracle
         ora = Oracle()
-        kc = kcache[0].cpu().numpy()
-        vc = vcache[0].cpu().numpy()
-        qn = in_host[0, :NH * HD].view(NH, HD).numpy()
+        n_cpu = min(4, n_layers)      # a bounded sample: 4 of the step's 16 layers
+        caches = [(kcache[l].cpu().numpy(), vcache[l].cpu().numpy()) for l in range(n_cpu)]
+        qs = [in_host[l, :NH * HD].view(NH, HD).numpy() for l in range(n_cpu)]
         t0 = time.perf_counter()
-        ora.attn(qn[None], kc, vc, [POS], NKV, SCALE, KT, VT)
+        for l in range(n_cpu):
+            ora.attn(qs[l][None], caches[l][0], caches[l][1], [POS], NKV, SCALE, KT, VT)
         dt = time.perf_counter() - t0
-        out["cpu_baseline"] = {"value": bytes_layer / dt / 1e9, "unit": "GB/s", "cores": ora.num_threads(),
-                               "kind": "port", "sample": "one layer-step (131001 keys) of the same workload, "
+        out["cpu_baseline"] = {"value": n_cpu * bytes_layer / dt / 1e9, "unit": "GB/s",
+                               "cores": ora.num_threads(), "kind": "port",
+                               "sample": f"{n_cpu} layer-steps (131001 keys each) of the same workload, "
                                "CPU oracle f32 attention, OpenMP over heads", "seconds": dt}
     if saved_stdout is not None:
         sys.stdout.flush()
