@@ -62,8 +62,8 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
              float *__restrict__ gate, const DecodeSeq *__restrict__ seqs, int rows_per_seq,
              const ExtraKey xk) {
   __shared__ float s_l[kMergeGroups];
+  __shared__ float s_gm[kMergeGroups];
   __shared__ float s_acc[kMergeGroups][kMergeDims];
-  __shared__ float s_mm;
   pdl_launch_dependents();
   pdl_wait();
 
@@ -106,43 +106,59 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     x_vrow = xk.v_row + (size_t)kvh * merge_row_bytes(xk.vt);
   }
 
-  // pass 1: the maximum over this output's records
-  float mx = MODE == 3 ? x_score : -INFINITY;
-  for (int s = lo + threadIdx.x; s < hi; s += blockDim.x) mx = fmaxf(mx, base[(size_t)s * kRec]);
+  // One pass: group ty walks records lo+ty, lo+ty+16, ... with four loads in flight and
+  // keeps a local log-sum-exp (m, l, acc); the 16 groups are then combined through shared
+  // memory. An empty record (m = -inf) weighs nothing and whatever its body holds is
+  // never used.
+  float mloc = -INFINITY, acc = 0.f, ll = 0.f;
+  for (int s0 = lo + ty; s0 < hi; s0 += 4 * kMergeGroups) {
+    float m4[4], a4[4], l4[4];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if ((threadIdx.x & 31) == 0) s_acc[0][threadIdx.x >> 5] = mx;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float m = -INFINITY;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, s_acc[0][i]);
-    s_mm = m;
-  }
-  __syncthreads();
-  const float mm = s_mm;
-  __syncthreads();
-
-  // pass 2: group ty walks records lo+ty, lo+ty+16, ...
-  float acc = 0.f, ll = 0.f;
-  if (mm != -INFINITY) {
-    for (int s = lo + ty; s < hi; s += kMergeGroups) {
-      const float *rec = base + (size_t)s * kRec;
-      const float w = expf(rec[0] - mm);  // an empty record (m = -inf) weighs 0
-      if (w > 0.f) {                      // ... and is never read, whatever it holds
-        acc = fmaf(rec[2 + quarter * kMergeDims + tx], w, acc);
-        if (tx == 0) ll = fmaf(rec[1], w, ll);
+    for (int k = 0; k < 4; ++k) {
+      const int s = s0 + k * kMergeGroups;
+      m4[k] = -INFINITY;
+      a4[k] = l4[k] = 0.f;
+      if (s < hi) {
+        const float *rec = base + (size_t)s * kRec;
+        m4[k] = rec[0];
+        a4[k] = rec[2 + quarter * kMergeDims + tx];
+        if (tx == 0) l4[k] = rec[1];
       }
+    }
+    const float mb = fmaxf(fmaxf(mloc, fmaxf(m4[0], m4[1])), fmaxf(m4[2], m4[3]));
+    if (mb != -INFINITY) {
+      const float f = expf(mloc - mb);   // 0 while nothing has been accumulated
+      acc *= f;
+      ll *= f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (m4[k] != -INFINITY) {
+          const float w = expf(m4[k] - mb);
+          acc = fmaf(a4[k], w, acc);
+          ll = fmaf(l4[k], w, ll);
+        }
+      }
+      mloc = mb;
     }
   }
   s_acc[ty][tx] = acc;
-  if (tx == 0) s_l[ty] = ll;
+  if (tx == 0) {
+    s_l[ty] = ll;
+    s_gm[ty] = mloc;
+  }
   __syncthreads();
   if (ty == 0) {
+    float mm = MODE == 3 ? x_score : -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMergeGroups; ++i) mm = fmaxf(mm, s_gm[i]);
     float a = 0.f, l = 0.f;
 #pragma unroll
     for (int i = 0; i < kMergeGroups; ++i) {
-      a += s_acc[i][tx];
-      l += s_l[i];
+      if (s_gm[i] != -INFINITY) {
+        const float w = expf(s_gm[i] - mm);
+        a = fmaf(s_acc[i][tx], w, a);
+        l = fmaf(s_l[i], w, l);
+      }
     }
     const int d = quarter * kMergeDims + tx;
     if (MODE == 3) {

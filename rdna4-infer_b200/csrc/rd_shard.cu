@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(kPushDims *kPushGroups)
 shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__restrict__ out,
                       float *__restrict__ gate, int n_head, ShardPeers g, DeviceStatus *status) {
   __shared__ float s_l[kPushGroups];
+  __shared__ float s_gm[kPushGroups];
   __shared__ float s_acc[kPushGroups][kPushDims];
-  __shared__ float s_mm;
 
   const int row = blockIdx.x, quarter = blockIdx.y;
   const int tx = threadIdx.x % kPushDims, ty = threadIdx.x / kPushDims;
@@ -103,42 +103,58 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
   const size_t part0 = (size_t)par * g.world * rstride + ((size_t)row * kQuarters + quarter) * kXPart;
 
   if (PUSH) {
+    // one pass, as in merge_kernel: group ty walks records ty, ty+16, ... with four loads
+    // in flight and a local log-sum-exp; the 16 groups meet in shared memory
     const float *base = partial + (size_t)row * n_in * kRec;
-    float mx = -INFINITY;
-    for (int s = threadIdx.x; s < n_in; s += blockDim.x) mx = fmaxf(mx, base[(size_t)s * kRec]);
+    float mloc = -INFINITY, acc = 0.f, ll = 0.f;
+    for (int s0 = ty; s0 < n_in; s0 += 4 * kPushGroups) {
+      float m4[4], a4[4], l4[4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((threadIdx.x & 31) == 0) s_acc[0][threadIdx.x >> 5] = mx;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float m = -INFINITY;
-      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, s_acc[0][i]);
-      s_mm = m;
-    }
-    __syncthreads();
-    const float mm = s_mm;
-    __syncthreads();
-
-    float acc = 0.f, ll = 0.f;
-    if (mm != -INFINITY) {
-      for (int s = ty; s < n_in; s += kPushGroups) {
-        const float *rec = base + (size_t)s * kRec;
-        const float w = expf(rec[0] - mm);
-        if (w > 0.f) {
-          acc = fmaf(rec[2 + d], w, acc);
-          if (tx == 0) ll = fmaf(rec[1], w, ll);
+      for (int k = 0; k < 4; ++k) {
+        const int sidx = s0 + k * kPushGroups;
+        m4[k] = -INFINITY;
+        a4[k] = l4[k] = 0.f;
+        if (sidx < n_in) {
+          const float *rec = base + (size_t)sidx * kRec;
+          m4[k] = rec[0];
+          a4[k] = rec[2 + d];
+          if (tx == 0) l4[k] = rec[1];
         }
+      }
+      const float mb = fmaxf(fmaxf(mloc, fmaxf(m4[0], m4[1])), fmaxf(m4[2], m4[3]));
+      if (mb != -INFINITY) {
+        const float f = expf(mloc - mb);
+        acc *= f;
+        ll *= f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (m4[k] != -INFINITY) {
+            const float w = expf(m4[k] - mb);
+            acc = fmaf(a4[k], w, acc);
+            ll = fmaf(l4[k], w, ll);
+          }
+        }
+        mloc = mb;
       }
     }
     s_acc[ty][tx] = acc;
-    if (tx == 0) s_l[ty] = ll;
+    if (tx == 0) {
+      s_l[ty] = ll;
+      s_gm[ty] = mloc;
+    }
     __syncthreads();
     if (ty == 0) {
+      float mm = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kPushGroups; ++i) mm = fmaxf(mm, s_gm[i]);
       float a = 0.f, l = 0.f;
 #pragma unroll
       for (int i = 0; i < kPushGroups; ++i) {
-        a += s_acc[i][tx];
-        l += s_l[i];
+        if (s_gm[i] != -INFINITY) {
+          const float w = expf(s_gm[i] - mm);
+          a = fmaf(s_acc[i][tx], w, a);
+          l = fmaf(s_l[i], w, l);
+        }
       }
       // every quarter carries its own copy of (m, l): part layout [m, l, 64 values]
       const size_t mine = part0 + (size_t)g.rank * rstride;
