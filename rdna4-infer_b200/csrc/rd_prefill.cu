@@ -276,30 +276,34 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     for (int rr = 0; rr < 16; ++rr) {
       const int r = warp * 16 + rr;      // row inside the tile
       const int gr = row0 + r;
-      float v[8];
+      float v[8], other[8];
+      // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
+      // l and l ^ (n_rot/16) at the same element index. Those lanes load their partner's
+      // eight values as well (same cache lines) instead of shuffling: a shuffle inside
+      // this loop keeps the compiler from batching the rows' global loads.
+      const int half_lanes = p.n_rot / 16;
+      const bool rot = pairs > 0 && lane < 2 * half_lanes;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = other[i] = 0.f;
       if (gr < p.n_q) {
-        const float4 *src =
-            reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim) + 2 * lane;
-        const float4 a = src[0], b = src[1];
+        const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim);
+        const float4 a = src[2 * lane], b = src[2 * lane + 1];
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        if (rot) {
+          const int pl = lane ^ half_lanes;
+          const float4 c = src[2 * pl], d = src[2 * pl + 1];
+          other[0] = c.x; other[1] = c.y; other[2] = c.z; other[3] = c.w;
+          other[4] = d.x; other[5] = d.y; other[6] = d.z; other[7] = d.w;
+        }
       }
-      if (pairs > 0) {
-        // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
-        // l and l ^ (n_rot/16) at the same element index
-        const int half_lanes = p.n_rot / 16;
+      if (rot) {
+        const bool lo = lane < half_lanes;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
-          if (lane < 2 * half_lanes) {
-            const bool lo = lane < half_lanes;
-            const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
-            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
-                      : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
-          }
+          const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
+          v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other[i], cs.y))
+                    : __fadd_rn(__fmul_rn(other[i], cs.y), __fmul_rn(v[i], cs.x));
         }
       }
       const uint32_t w0 = pack_h2(v[0] * p.qscale, v[1] * p.qscale);
@@ -580,22 +584,43 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       }
       asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
       // 128 threads: 8 rows x 16 chunks per pass
+      if (p.gate == nullptr) {
 #pragma unroll 8
-      for (int pass = 0; pass < kPfM / 8; ++pass) {
-        const int rr = pass * 8 + (gt >> 4), q = gt & 15;
-        const int gr = row0 + rr;
-        if (gr < p.n_q) {
-          float4 v = *reinterpret_cast<const float4 *>(gstg + rr * 256 + ((q ^ (rr & 15)) << 4));
-          const size_t off = ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q;
-          if (p.gate != nullptr) {
-            const float4 g = *reinterpret_cast<const float4 *>(p.gate + off);
-            // fast exp/divide: ~1e-6 relative, far inside the attention tolerance
-            v.x *= __fdividef(1.0f, 1.0f + __expf(-g.x));
-            v.y *= __fdividef(1.0f, 1.0f + __expf(-g.y));
-            v.z *= __fdividef(1.0f, 1.0f + __expf(-g.z));
-            v.w *= __fdividef(1.0f, 1.0f + __expf(-g.w));
+        for (int pass = 0; pass < kPfM / 8; ++pass) {
+          const int rr = pass * 8 + (gt >> 4), q = gt & 15;
+          const int gr = row0 + rr;
+          if (gr < p.n_q)
+            *reinterpret_cast<float4 *>(p.out + ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q) =
+                *reinterpret_cast<const float4 *>(gstg + rr * 256 + ((q ^ (rr & 15)) << 4));
+        }
+      } else {
+        // the gate values of 4 passes are requested together before any store (out and gate
+        // may alias as far as the compiler knows, so it would otherwise wait for every load
+        // behind the previous store)
+        for (int p0 = 0; p0 < kPfM / 8; p0 += 4) {
+          float4 gv[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int rr = (p0 + k) * 8 + (gt >> 4), gr = row0 + rr;
+            gv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gr < p.n_q)
+              gv[k] = *reinterpret_cast<const float4 *>(p.gate + ((size_t)gr * p.n_head + head) * kHeadDim +
+                                                        64 * c + 4 * (gt & 15));
           }
-          *reinterpret_cast<float4 *>(p.out + off) = v;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int rr = (p0 + k) * 8 + (gt >> 4), q = gt & 15;
+            const int gr = row0 + rr;
+            if (gr < p.n_q) {
+              float4 v = *reinterpret_cast<const float4 *>(gstg + rr * 256 + ((q ^ (rr & 15)) << 4));
+              // fast exp/divide: ~1e-6 relative, far inside the attention tolerance
+              v.x *= __fdividef(1.0f, 1.0f + __expf(-gv[k].x));
+              v.y *= __fdividef(1.0f, 1.0f + __expf(-gv[k].y));
+              v.z *= __fdividef(1.0f, 1.0f + __expf(-gv[k].z));
+              v.w *= __fdividef(1.0f, 1.0f + __expf(-gv[k].w));
+              *reinterpret_cast<float4 *>(p.out + ((size_t)gr * p.n_head + head) * kHeadDim + 64 * c + 4 * q) = v;
+            }
+          }
         }
       }
       asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
