@@ -381,6 +381,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--fused-append", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"], help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -482,6 +483,12 @@ def main():
     def layer_step(l, host_io):
         st = rd.stream_ptr()   # the capturing stream while a graph is being recorded
         n = 0
+        if world == 1 and args.fused_append:    # two launches per layer-step instead of three
+            rd.check(L.rd_attn_decode_append_ws(rd.ptr(q_dev[l]), rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
+                                                rd.ptr(kcache[l]), rd.ptr(vcache[l]), rd.ptr(o_dev[l]), POS, NH,
+                                                NKV, HD, SCALE, KT, VT, rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
+                                                st))
+            return 2
         if owns_new_row:
             off = (POS - kb) * NKV * row
             rd.check(L.rd_kv_append(KT, VT, rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
