@@ -468,7 +468,7 @@ def main():
                 dist.barrier()
                 group = rd.shard_group(rank, [int(p) for p in hdl.buffer_ptrs])
                 group._tensor, group._handle = xbuf, hdl
-                exchange = "peer stores + flags (fused into the merge kernels)"
+                exchange = "peer stores of epoch-tagged words, fused into the merge kernels"
             except Exception as e:
                 if rank == 0:
                     print(f"# symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
