@@ -377,10 +377,8 @@ int rd_attn_plan(int n_keys, int n_tok, int n_head_kv, int k_type, int v_type, i
     sm_count = ::sm_count(dev);
   }
   const int tile = decode_tile_keys(k_type, v_type);
-  const int stage_bytes = tile * (key_pitch(k_type, n_head_kv) + key_pitch(v_type, n_head_kv));
-  int stages = (kSmemBudget - kRingOffset) / stage_bytes;
+  const int stages = ring_depth(k_type, v_type, n_head_kv);
   if (stages < 1) return RD_ERR_UNSUPPORTED;
-  if (stages > kMaxStages) stages = kMaxStages;
   const int64_t tiles = ((int64_t)n_keys + tile - 1) / tile;
   if (tile_keys != nullptr) *tile_keys = tile;
   if (ring_stages != nullptr) *ring_stages = stages;

@@ -53,31 +53,43 @@ struct DeviceStatus {
 };
 
 // ---- decode tile geometry (shared by the kernel and the host-side split planning)
-constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 220 * 1024;  // per CTA, of the 227 KB an sm_100 CTA may use
+// A CTA of the decode kernel runs G key groups of four warps (one per kv head); group gi
+// streams 16-key slots through its own ring of D shared-memory slots.
+constexpr int kMaxStages = 8;            // ring depth per key group
+constexpr int kMaxGroups = 3;
+constexpr int kSmemBudget = 225 * 1024;  // dynamic, per CTA, of the 227 KB an sm_100 CTA may use
+constexpr int kSlotKeys = 16;            // keys per ring slot = rows of one MMA tile
 
 // Bytes of one key in a shared-memory tile: the n_head_kv rows plus 16 bytes, which
 // makes the per-lane row walks of every loader above bank-conflict-free for
 // n_head_kv == 4 (pitch = 16 or 80 bytes mod 128).
 __host__ __device__ constexpr int key_pitch(int type, int nkv) { return nkv * row_bytes(type) + 16; }
 
-// Shared memory in front of the tile ring: 16 mbarriers, then the query rows of the
-// CTA's token pre-scaled in f32, [head][260] with dim d at d + (d >> 6) (the skew keeps
-// the fragment build free of bank conflicts).
-constexpr int kQRowFloats = 260;
-constexpr int kQStageBytes = 4 * kGroup * kQRowFloats * 4;       // n_head_kv <= 4
-constexpr int kRingOffset = 16 * kMaxStages + kQStageBytes;      // multiple of 128
+// Shared memory in front of the ring: the slots' mbarriers and counters (512 bytes),
+// then the query fragments of the CTA's token: a 256-entry dim -> slot table (512
+// bytes) and 144 bytes per (head, quad lane) for up to 24 heads.
+constexpr int kBarBytes = 512;
+constexpr int kFragPitch = 144;
+constexpr int kQStageBytes = 512 + 4 * kGroup * 4 * kFragPitch;   // n_head_kv <= 4
+constexpr int kRingOffset = kBarBytes + kQStageBytes;             // multiple of 128
+static_assert(kRingOffset % 128 == 0, "ring must start 128-byte aligned");
 
-// 16-key groups per tile = consumer warps per kv head: as many (up to 3) as leave room
-// for three stages -- more resident warps hide the dequantize -> MMA latency better.
-__host__ __device__ constexpr int key_groups(int kt, int vt) {
-  return 3 * 48 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget - kRingOffset   ? 3
-         : 3 * 32 * (key_pitch(kt, 4) + key_pitch(vt, 4)) <= kSmemBudget - kRingOffset ? 2
-                                                                                       : 1;
+__host__ __device__ constexpr int slot_bytes(int kt, int vt, int nkv) {
+  return kSlotKeys * (key_pitch(kt, nkv) + key_pitch(vt, nkv));
 }
-// Floats of one warp's slot in the epilogue staging: 6 heads x (m, l, 8 blocks x 33).
-constexpr int kStgHead = 2 + 8 * 33;
-constexpr int kStgWarp = kGroup * kStgHead;
+// Key groups per CTA: as many (up to 3) as leave every group a ring of at least two
+// slots -- more resident warps hide the dequantize -> MMA latency better, and two slots
+// per group keep one load in flight while the other slot is consumed.
+__host__ __device__ constexpr int key_groups(int kt, int vt) {
+  return 3 * 2 * slot_bytes(kt, vt, 4) <= kSmemBudget - kRingOffset   ? 3
+         : 2 * 2 * slot_bytes(kt, vt, 4) <= kSmemBudget - kRingOffset ? 2
+                                                                      : 1;
+}
+// Ring depth per group for n_head_kv kv heads (0: one slot does not fit).
+__host__ __device__ constexpr int ring_depth(int kt, int vt, int nkv) {
+  const int d = (kSmemBudget - kRingOffset) / (key_groups(kt, vt) * slot_bytes(kt, vt, nkv));
+  return d > kMaxStages ? kMaxStages : d;
+}
 
 // ---- programmatic dependent launch ---------------------------------------------
 // The hot kernels of a layer step (append, decode, merge) are launched with the

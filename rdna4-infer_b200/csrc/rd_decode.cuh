@@ -5,10 +5,12 @@
 // and the unsplit attn_kernel, :95-185):
 //   * grid (n_splits, n_tok): CTA s owns a contiguous slice of the key tiles and
 //     writes one partial record (m, l, acc[256]) per query head;
-//   * a producer warp streams tiles of TILE keys into a ring of shared-memory stages
-//     with one bulk (TMA-engine) copy per key and tensor -- the n_head_kv rows of a
-//     key are contiguous in the cache -- completion counted on an mbarrier;
-//   * consumer warp (kv head, 16-key group) dequantizes its rows IN REGISTERS straight
+//   * the CTA's warps form key groups of four (one warp per kv head); every group streams
+//     16-key slots through its own ring in shared memory -- one tensor-map (TMA) copy per
+//     slot and tensor, the n_head_kv rows of a key being contiguous in the cache, or one
+//     bulk copy per key for wide rows -- completion counted on an mbarrier; the warp that
+//     finishes a slot last issues the slot's next load, so no warp is only a producer;
+//   * warp (kv head, key group) dequantizes its rows IN REGISTERS straight
 //     into mma.sync m16n8k16 f16 fragments: QK^T with the 16 keys on M and the 6 heads
 //     (padded to 8) on N, then P*V with V^T on M (dims) and the keys on K. The
 //     arithmetic intensity of q4_0 (21 flop/byte) is beyond the FP32 pipe at HBM
@@ -327,6 +329,9 @@ struct KLoad<RD_KV_Q4_1> {
 // =============================== V loaders =======================================
 // A fragment of V^T*P for M-tile m (0..15): rows g / g+8 = two true dims chosen by
 // the loader (dim(g, m, r)), k-slots = keys (2t, 2t+1, 2t+8, 2t+9) of the group.
+// kPairM says which two accumulator values of a lane are neighbours in memory (the
+// epilogue stores them as one 8-byte word): true, dim(g, m + 1, r) = dim(g, m, r) + 1 for
+// even m; false, dim(g, m, 1) = dim(g, m, 0) + 1. Either way the first dim is even.
 // rows[j] is the shared address of the stored row of key j of those four. run()
 // calls mma(m, a0, a1, a2, a3) for m = 0..15. Values come out multiplied by 1/kUnscale.
 template <int T>
@@ -334,6 +339,7 @@ struct VLoad;
 
 template <>
 struct VLoad<RD_KV_Q4_0> {
+  static constexpr bool kPairM = true;
   static constexpr float kUnscale = kQuantUnscale;
   // lane g owns block g of each key: 18 bytes at 18g, read as 5 aligned words from
   // (18g & ~3); for odd g the block starts in the upper half of the first word.
@@ -377,6 +383,7 @@ struct VLoad<RD_KV_Q4_0> {
 
 template <>
 struct VLoad<RD_KV_Q8_0> {
+  static constexpr bool kPairM = false;
   static constexpr float kUnscale = kQuantUnscale;
   // lane g owns block g: 34 bytes at 34g, read as 9 aligned words from (34g & ~3).
   __device__ static int hidx(int s, int par) { return s <= 14 ? s + 1 - par : (par ? 15 : 0); }
@@ -418,6 +425,7 @@ struct VLoad<RD_KV_Q8_0> {
 
 template <>
 struct VLoad<RD_KV_F16> {
+  static constexpr bool kPairM = false;
   static constexpr float kUnscale = 1.0f;
   // lane g owns the 16-byte chunks g + 8*ci, ci = 0..3, of each key.
   __device__ static int dim(int g, int m, int r) { return 8 * (g + 8 * (m >> 2)) + 2 * (m & 3) + r; }
@@ -442,6 +450,7 @@ struct VLoad<RD_KV_F16> {
 
 template <>
 struct VLoad<RD_KV_F32> {
+  static constexpr bool kPairM = false;
   static constexpr float kUnscale = 1.0f;
   // lane g owns the 16-byte chunks (4 dims) g + 8*ci, ci = 0..7.
   __device__ static int dim(int g, int m, int r) { return 4 * (g + 8 * (m >> 1)) + 2 * (m & 1) + r; }
@@ -464,6 +473,7 @@ struct VLoad<RD_KV_F32> {
 
 template <>
 struct VLoad<RD_KV_Q5_0> {
+  static constexpr bool kPairM = true;
   static constexpr float kUnscale = kQuantUnscale;
   // lane g owns block g of each key: 22 bytes at 22g, read as six aligned words from
   // (22g & ~3); for odd g the block starts in the upper half of the first word, which
@@ -509,6 +519,7 @@ struct VLoad<RD_KV_Q5_0> {
 };
 template <>
 struct VLoad<RD_KV_Q4_1> {
+  static constexpr bool kPairM = true;
   static constexpr float kUnscale = kQuantUnscale;
   // lane g owns block g of each key: 20 bytes at 20g = five aligned words.
   __device__ static int dim(int g, int m, int r) { return 32 * g + m + 16 * r; }
@@ -539,7 +550,7 @@ struct VLoad<RD_KV_Q4_1> {
 
 // =============================== kernel ==========================================
 struct DecodeKernelArgs {
-  // Tensor maps over the K / V caches (see encode_kv_tmap): one box = one tile of TILE
+  // Tensor maps over the K / V caches (see encode_kv_tmap): one box = one slot of 16
   // keys in the padded shared-memory layout; used when k_tmap / v_tmap is set.
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
@@ -555,9 +566,12 @@ struct DecodeKernelArgs {
   int n_head;
   int nkv;
   float qscale;  // scale * log2(e)
-  int stages;
-  int debug;  // 0 normal; timing experiments only, bit mask: 1 consumers skip all math, 2 producer
-              // skips the copies, 4 skip QK, 8 skip PV, 16 skip the softmax
+  int depth;     // ring slots per key group
+  int group_bytes;  // shared memory per key group: its ring, at least one epilogue plane
+#ifdef RD_TIMING_SWITCHES
+  int debug;  // timing experiments only, bit mask: 1 skip all math, 2 skip the copies, 4 skip QK,
+              // 8 skip PV, 32 thread 0 overwrites its first record with clock readings
+#endif
   DeviceStatus *status;
   // Multi-sequence launches (MULTI): one CTA per work item (sequence, token, split);
   // everything per-sequence comes from the descriptor instead of the fields above.
@@ -571,12 +585,39 @@ struct DecodeKernelArgs {
   int new_row;
 };
 
+// acq_rel: the slot reads of the arriving warp happen before the refill the last
+// arriver issues.
+__device__ __forceinline__ uint32_t atom_add_acq_rel_shared(uint32_t addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_global_f2(float *p, float a, float b) {
+  *reinterpret_cast<float2 *>(p) = make_float2(a, b);
+}
+
+// Warps: 4 per key group (one per kv head), G groups. Nobody is only a producer: the
+// warp that is last to finish a slot re-arms it and issues the slot's next load, so a
+// CTA of 12 warps leaves each of them 168 registers (13 warps would cap them at 128:
+// the register file is split four ways and one quarter would hold four warps).
+//
+// Softmax reference: p = exp2(s - m) is taken against a reference m that is only moved
+// (and the accumulators rescaled) when a score exceeds it by more than kRefSlack, so
+// p <= 2^kRefSlack -- exact enough in f16 and far from overflow -- and the rescale runs
+// once or twice per CTA instead of on every new maximum. The true running maximum is
+// kept per lane and becomes the record's m at the end.
+constexpr float kRefSlack = 8.0f;
+constexpr int kPlaneHead = 268;   // floats per head in the epilogue planes (12 mod 32)
+
 template <int KT, int VT, bool MULTI>
-__global__ void __launch_bounds__((4 * key_groups(KT, VT) + 1) * 32, 1)
+__global__ void __launch_bounds__(4 * key_groups(KT, VT) * 32, 1)
 decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
-  constexpr int KG = key_groups(KT, VT);
-  constexpr int TILE = 16 * KG;
-  constexpr int CW = 4 * KG;  // consumer warps; warp CW is the producer
+  constexpr int G = key_groups(KT, VT);
+  constexpr int NW = 4 * G;
+  constexpr int NT = NW * 32;
   constexpr int RK = row_bytes(KT), RV = row_bytes(VT);
   using KL = KLoad<KT>;
   using VL = VLoad<VT>;
@@ -584,22 +625,72 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
 
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
+  // per (group, kv head * 8 + column): softmax reference, true maximum, row sum
+  __shared__ float s_m[kMaxGroups][32], s_t[kMaxGroups][32], s_l[kMaxGroups][32];
   pdl_launch_dependents();
+  if constexpr (!MULTI) {
+    // the tensor maps are kernel parameters: start fetching them now
+    if (threadIdx.x == 0 && p.k_tmap) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_k) : "memory");
+    if (threadIdx.x == 32 && p.v_tmap) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_v) : "memory");
+  }
+#ifdef RD_TIMING_SWITCHES
+  long long tr[8];
+  unsigned long long gt0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
+  tr[0] = clock64();
+#define RD_TRACE(i) tr[i] = clock64()
+#else
+#define RD_TRACE(i)
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
+  const int gi = warp >> 2, kvh = warp & 3;
   const int nkv = p.nkv;
+  const bool active = kvh < nkv;
+  const int D = p.depth;
   const int pitch_k = nkv * RK + 16, pitch_v = nkv * RV + 16;
-  const uint32_t stage_bytes = (uint32_t)TILE * (pitch_k + pitch_v);
-  // Shared-memory tile layout of both tensors: [key][the kv heads' rows + 16 bytes],
-  // written either by one tensor-map copy per tile or by one bulk copy per key.
-  const uint32_t k_key_stride = pitch_k, k_head_stride = RK;
-  const uint32_t v_key_stride = pitch_v, v_head_stride = RV;
-  const uint32_t v_tile_off = TILE * pitch_k;
-  const uint32_t bar_full = smem_u32(smem);                  // kMaxStages x 8 bytes
-  const uint32_t bar_empty = bar_full + 8 * kMaxStages;      // kMaxStages x 8 bytes
-  float *qstage = reinterpret_cast<float *>(smem + 16 * kMaxStages);
-  const uint32_t tiles0 = bar_full + kRingOffset;            // 128-byte aligned
+  const uint32_t slot_sz = (uint32_t)kSlotKeys * (pitch_k + pitch_v);
+  const uint32_t v_slot_off = kSlotKeys * pitch_k;
+  // Shared-memory layout: ring position (group, d) = index group * D + d owns a full
+  // barrier, an arrival counter, a fill count and the number of the slot it holds; then
+  // the query fragments; then the rings, group
+  // after group (p.group_bytes apart: a group's ring also holds its epilogue plane).
+  const uint32_t bar_full = smem_u32(smem);                       // 24 x 8 bytes
+  const uint32_t cnt0 = bar_full + 8 * kMaxGroups * kMaxStages;   // 24 x 4 bytes
+  const uint32_t nfill0 = cnt0 + 4 * kMaxGroups * kMaxStages;     // 24 x 4 bytes
+  const uint32_t sid0 = nfill0 + 4 * kMaxGroups * kMaxStages;     // 24 x 4 bytes: slot held, or -1
+  uint8_t *qstage = smem + kBarBytes;
+  const uint32_t ring0 = bar_full + kRingOffset;                  // 128-byte aligned
+  const uint32_t group_bytes = (uint32_t)p.group_bytes;
+
+  // ---- set-up that needs nothing from global memory --------------------------------
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < G * D; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      sts32(cnt0 + 4 * i, 0u);
+      sts32(nfill0 + 4 * i, 0u);
+    }
+    fence_barrier_init();
+  }
+  // Query fragments. Lane (g, tq) of every warp of a kv head needs the same 32 words:
+  // head g's values at the dims KL::dim(tq, n, 0..3), n = 0..15, as f16 pairs pre-scaled
+  // into log2 units (and by the loader's fixed-point factor). The threads build them
+  // cooperatively: a 256-entry table inverts KL::dim (dim -> fragment slot), every thread
+  // then loads query values coalesced and drops each as an f16 into its slot, 144 bytes
+  // per (head, tq), and every lane reads its 32 words with 8 conflict-free 16-byte loads
+  // -- instead of 64 scalar gathers per lane, repeated by every key-group warp.
+  unsigned short *inv = reinterpret_cast<unsigned short *>(qstage);           // 512 bytes
+  const uint32_t frag0 = smem_u32(qstage) + 512;
+  for (int i = threadIdx.x; i < 256; i += NT) {
+    const int tq_i = i >> 6, n_i = (i >> 2) & 15, e_i = i & 3;
+    // byte offset of the half inside the (head, tq) block: word 2n + (e >> 1), half e & 1
+    inv[KL::dim(tq_i, n_i, e_i)] = (unsigned short)(tq_i * kFragPitch + (2 * n_i + (e_i >> 1)) * 4 +
+                                                    (e_i & 1) * 2);
+  }
+  pdl_wait();   // everything below reads what earlier kernels of the stream wrote
+  RD_TRACE(1);
 
   // What this CTA works on: token qt, split s of S, keys key_begin..t_last of the caches
   // at kbase / vbase (or behind the tensor maps tmk / tmv), one record per head at
@@ -609,15 +700,6 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   const uint8_t *kbase, *vbase;
   const CUtensorMap *tmk, *tmv;
   float *rec0;
-  if (threadIdx.x == 0) {   // barriers first: they need nothing from global memory
-    s_abort = 0;
-    for (int i = 0; i < p.stages; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, CW);
-    }
-    fence_barrier_init();
-  }
-  pdl_wait();   // everything below reads what earlier kernels of the stream wrote
   if constexpr (MULTI) {
     const int4 item = p.items[blockIdx.x];
     const DecodeSeq &d = p.seqs[item.x];
@@ -634,6 +716,15 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     tmk = reinterpret_cast<const CUtensorMap *>(d.tm_k);
     tmv = reinterpret_cast<const CUtensorMap *>(d.tm_v);
     rec0 = p.partial + ((size_t)d.rec_base + (size_t)qt * p.n_head * S + s) * kRec;
+    // These descriptors were written to global memory by an ordinary copy and may have
+    // been rewritten since an earlier launch read them: make the copy visible to the
+    // tensor-map proxy of every thread that may issue a load through them.
+    if (lane == 0 || lane == 16) {
+      if (use_tk)
+        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmk) : "memory");
+      if (use_tv)
+        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmv) : "memory");
+    }
   } else {
     qt = blockIdx.y;
     s = blockIdx.x;
@@ -649,22 +740,102 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     tmv = &p.tm_v;
     rec0 = p.partial + ((size_t)qt * p.n_head * S + s) * kRec;
   }
+  // Key split in 16-key slots: CTA s owns slots [c_b, c_e) of the attended range and
+  // deals them round-robin to its key groups (group x: local slots x, x + G, ...), so the
+  // order of every sum is fixed by the shape alone.
   const int n_keys = t_last >= key_begin ? t_last - key_begin + 1 : 0;
-  const int tiles_total = (n_keys + TILE - 1) / TILE;
-  const int tile_b = (int)(((int64_t)tiles_total * s) / S);
-  const int tile_e = (int)(((int64_t)tiles_total * (s + 1)) / S);
-  const int ntiles = tile_e - tile_b;
-  const int key0 = key_begin + tile_b * TILE;
+  const int slots_total = (n_keys + kSlotKeys - 1) / kSlotKeys;
+  const int c_b = (int)(((int64_t)slots_total * s) / S);
+  const int c_e = (int)(((int64_t)slots_total * (s + 1)) / S);
+  const int n_slots = c_e - c_b;
+  const int key0 = key_begin + c_b * kSlotKeys;
+  const uint32_t kb = (uint32_t)nkv * RK, vb = (uint32_t)nkv * RV;
 
-  __syncthreads();
-  // Fused append: the newest position's K and V rows are quantized by the consumer warps
-  // of the first CTAs (one 32-value block per warp) while the first tiles are in flight.
+  // The query rows of this token: requested before anything else, so that they do not
+  // queue behind the first lap of slot loads.
+  const float4 *q4 = reinterpret_cast<const float4 *>(qsrc);
+  const int n_q4 = nkv * kGroup * (kHeadDim / 4);
+  float4 qv[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + j * NT;
+    qv[j] = i < n_q4 ? q4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  // Loads group fgi's next slot for ring position d -- on the position's lap-th fill
+  // that is the group's slot lap * D + d -- or, once the group's slots have run out,
+  // completes the position empty (slot number -1), which is the group's signal to stop.
+  // Warp-collective.
+  auto fill = [&](int fgi, int d) {
+    const int pos = fgi * D + d;
+    const uint32_t bar = bar_full + 8 * pos;
+    const uint32_t sk = ring0 + fgi * group_bytes + d * slot_sz, sv = sk + v_slot_off;
+    int c = 0;
+    if (lane == 0) {
+      const uint32_t lap = lds32(nfill0 + 4 * pos);
+      c = fgi + G * ((int)lap * D + d);
+      if (c >= n_slots) c = -1;
+      sts32(sid0 + 4 * pos, (uint32_t)c);
+      sts32(nfill0 + 4 * pos, lap + 1u);
+#ifdef RD_TIMING_SWITCHES
+      if (c >= 0 && (p.debug & 2)) {   // no copies: the barrier completes at once
+        mbar_arrive(bar);
+        c = -1;
+      } else
+#endif
+      if (c < 0)
+        mbar_arrive(bar);
+      else  // a tensor-map box counts its zero-filled padding columns too
+        mbar_expect_tx(bar, kSlotKeys * ((use_tk ? pitch_k : kb) + (use_tv ? pitch_v : vb)));
+    }
+    c = __shfl_sync(FULL, c, 0);
+    if (c < 0) return;
+    const int row0 = key0 + c * kSlotKeys;
+    if (use_tk) {
+      if (lane == 0) tma_load_2d(sk, tmk, 0, row0, bar);
+    } else if (lane < kSlotKeys) {
+      const int key = row0 + lane > t_last ? t_last : row0 + lane;  // tail rows repeat the last key
+      bulk_g2s(sk + lane * pitch_k, kbase + (size_t)key * kb, kb, bar);
+    }
+    if (use_tv) {
+      if (lane == 16) tma_load_2d(sv, tmv, 0, row0, bar);
+    } else if (lane >= 16) {
+      const int key = row0 + lane - 16 > t_last ? t_last : row0 + lane - 16;
+      bulk_g2s(sv + (lane - 16) * pitch_v, vbase + (size_t)key * vb, vb, bar);
+    }
+  };
+
+  __syncthreads();   // barriers, counters and the table are in place
+  // every group's first slot first; the rest of the first lap follows the query build
+  if (warp == 0)
+    for (int fgi = 0; fgi < G; ++fgi) fill(fgi, 0);
+  {
+    const float qmul = p.qscale * KL::kUnscale;
+    auto scatter = [&](int i, const float4 &v) {
+      const int head = i >> 6, c4 = i & 63;
+      const uint32_t hb = frag0 + (uint32_t)head * (4 * kFragPitch);
+      const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned short hbits = __half_as_ushort(__float2half_rn(x[j] * qmul));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(hb + inv[4 * c4 + j]), "h"(hbits) : "memory");
+      }
+    };
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * NT;
+      if (i < n_q4) scatter(i, qv[j]);
+    }
+    for (int i = threadIdx.x + 4 * NT; i < n_q4; i += NT) scatter(i, q4[i]);   // G < 3 only
+  }
+  // Fused append: the newest position's K and V rows are quantized by the warps of the
+  // first CTAs (one 32-value block per warp) while the first slots are in flight.
   // Nobody in this launch reads that row: the keys attended end before it, and the merge
   // that follows folds it in from the cache.
   if constexpr (!MULTI) {
-    if (p.k_new != nullptr && warp < CW && blockIdx.y == 0) {
+    if (p.k_new != nullptr && blockIdx.y == 0) {
       const int per_tensor = nkv * (kHeadDim / 32);
-      for (int b = (int)blockIdx.x * CW + warp; b < 2 * per_tensor; b += (int)gridDim.x * CW) {
+      for (int b = (int)blockIdx.x * NW + warp; b < 2 * per_tensor; b += (int)gridDim.x * NW) {
         if (b < per_tensor)
           store_block<KT>(p.k_new[b * 32 + lane], const_cast<uint8_t *>(p.k) + (size_t)p.new_row * nkv * RK, b,
                           lane);
@@ -674,100 +845,24 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
       }
     }
   }
-  // Query fragments. Lane (g, tq) of every consumer warp of a kv head needs the same 32
-  // words: head g's values at the dims KL::dim(tq, n, 0..3), n = 0..15, as f16 pairs
-  // pre-scaled into log2 units (and by the loader's fixed-point factor). The consumer
-  // threads build them cooperatively: a 256-entry table inverts KL::dim (dim -> fragment
-  // slot), every thread then loads query values coalesced and drops each as an f16 into
-  // its slot, 144 bytes per (head, tq), and every lane reads its 32 words with 8
-  // conflict-free 16-byte loads -- instead of 64 scalar gathers per lane, repeated by
-  // every key-group warp.
-  constexpr int kFragPitch = 144;   // bytes per (head, tq): 32 words + 16 of padding
-  unsigned short *inv = reinterpret_cast<unsigned short *>(qstage);           // 512 bytes
-  const uint32_t frag0 = smem_u32(qstage) + 512;
-  if (warp < CW) {
-    for (int i = threadIdx.x; i < 256; i += CW * 32) {
-      const int tq_i = i >> 6, n_i = (i >> 2) & 15, e_i = i & 3;
-      // byte offset of the half inside the (head, tq) block: word 2n + (e >> 1), half e & 1
-      inv[KL::dim(tq_i, n_i, e_i)] = (unsigned short)(tq_i * kFragPitch + (2 * n_i + (e_i >> 1)) * 4 +
-                                                      (e_i & 1) * 2);
-    }
-    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
-    const float qmul = p.qscale * KL::kUnscale;
-    const float4 *q4 = reinterpret_cast<const float4 *>(qsrc);
-    for (int i = threadIdx.x; i < nkv * kGroup * (kHeadDim / 4); i += CW * 32) {
-      const int head = i >> 6, c4 = i & 63;
-      const float4 v = q4[i];
-      const uint32_t hb = frag0 + (uint32_t)head * (4 * kFragPitch);
-      const float x[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const unsigned short hbits = __half_as_ushort(__float2half_rn(x[j] * qmul));
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(hb + inv[4 * c4 + j]), "h"(hbits) : "memory");
-      }
-    }
-    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
-  }
+  __syncthreads();
+  RD_TRACE(2);
+  // rest of the first lap: ring position x of a group by the group's warp x & 3
+  for (int x = 1; x < D; ++x)
+    if ((x & 3) == kvh) fill(gi, x);
 
-  // ---- per-warp state (consumers) ----
-  const int kvh = warp % nkv, gi = warp / nkv;
-  const bool active = warp < CW && gi < KG;
+  // ---- per-warp state ----
   float O[16][4];
-  // Running maxima start at a large finite negative instead of -inf: exp2(m_old - m_new)
-  // and exp2(s - m) then need no special cases (an all-masked step keeps p = 0).
+  // Maxima start at a large finite negative instead of -inf: exp2(m_old - m_new) and
+  // exp2(s - m) then need no special cases (an all-masked step keeps p = 0).
   constexpr float kNegBig = -1.0e30f;
-  float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
+  float m0 = kNegBig, m1 = kNegBig;       // softmax references of the lane's two head columns
+  float run0 = kNegBig, run1 = kNegBig;   // lane-local true maxima
+  float l0 = 0.f, l1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
 
-  if (warp == CW) {
-    // =========================== producer =======================================
-    const uint32_t kb = (uint32_t)nkv * RK, vb = (uint32_t)nkv * RV;
-    int st = 0;
-    uint32_t ph = 1;  // parity of the previous use of the stage (no wait on the first lap)
-    for (int it = 0; it < ntiles; ++it, ++st) {
-      if (st == p.stages) {
-        st = 0;
-        ph ^= 1;
-      }
-      if (it >= p.stages) {
-        if (!mbar_wait(bar_empty + 8 * st, ph, p.status, 1)) {
-          s_abort = 1;
-          break;
-        }
-      }
-      if (*(volatile int *)&s_abort) break;
-      const uint32_t full = bar_full + 8 * st;
-      // a tensor-map box counts its zero-filled padding columns too
-      if (p.debug & 2) {
-        if (lane == 0) mbar_arrive(full);
-        continue;
-      }
-      if (lane == 0)
-        mbar_expect_tx(full, TILE * ((use_tk ? pitch_k : kb) + (use_tv ? pitch_v : vb)));
-      __syncwarp();
-      const uint32_t sk = tiles0 + st * stage_bytes;
-      const uint32_t sv = sk + v_tile_off;
-      const int row0 = key0 + it * TILE;
-      if (use_tk) {
-        if (lane == 0) tma_load_2d(sk, tmk, 0, row0, full);
-      } else {
-        for (int kk = lane; kk < TILE; kk += 32) {   // TILE is 16, 32 or 48
-          const int key = row0 + kk > t_last ? t_last : row0 + kk;  // tail rows repeat the last key
-          bulk_g2s(sk + kk * pitch_k, kbase + (size_t)key * kb, kb, full);
-        }
-      }
-      if (use_tv) {
-        if (lane == 0) tma_load_2d(sv, tmv, 0, row0, full);
-      } else {
-        for (int kk = lane; kk < TILE; kk += 32) {
-          const int key = row0 + kk > t_last ? t_last : row0 + kk;
-          bulk_g2s(sv + kk * pitch_v, vbase + (size_t)key * vb, vb, full);
-        }
-      }
-    }
-  } else if (active) {
-    // =========================== consumers ======================================
+  if (active) {
     // Q fragments (B operand): lane (g, tq) holds head g's 32 words; padding heads are 0.
     uint32_t qb[16][2];
     {
@@ -782,266 +877,228 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
         qb[2 * i + 1][1] = g < kGroup ? v.w : 0u;
       }
     }
-
-    // One step consumes the warp's 16-key group of NG consecutive tiles. Two groups per
-    // step give the scheduler two independent dequantize->MMA streams per warp (there
-    // are only two consumer warps per scheduler) and halve the softmax bookkeeping.
-    int cst = 0;        // ring stage of the next tile to consume
-    uint32_t cph = 0;   // and the parity its full barrier completes with
-    auto step = [&](auto ngc, const int it0) -> bool {
-      constexpr int NG = decltype(ngc)::value;
-      uint32_t sk[NG], sv[NG], bar_e[NG];
-      int kbase[NG];
-#pragma unroll
-      for (int j = 0; j < NG; ++j) {
-        if (!mbar_wait(bar_full + 8 * cst, cph, p.status, 2)) return false;
-        sk[j] = tiles0 + cst * stage_bytes;
-        sv[j] = sk[j] + v_tile_off;
-        bar_e[j] = bar_empty + 8 * cst;
-        kbase[j] = key0 + (it0 + j) * TILE + 16 * gi;  // first key of this warp's group
-        if (++cst == p.stages) {
-          cst = 0;
-          cph ^= 1;
-        }
+    const uint32_t my_ring = ring0 + gi * group_bytes;
+    const uint32_t k_row_off = (uint32_t)g * pitch_k + kvh * RK;
+    const uint32_t v_row_off = (uint32_t)(2 * tq) * pitch_v + kvh * RV;
+    int d = 0;         // ring position of the next slot to consume
+    uint32_t ph = 0;   // and the parity its full barrier completes with
+    for (int i = 0;; ++i) {
+      const int slot = gi * D + d;
+      if (!mbar_wait(bar_full + 8 * slot, ph, p.status, 2)) {
+        s_abort = 1;
+        break;
       }
-
-      if (p.debug & 1) {
-        __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int j = 0; j < NG; ++j) mbar_arrive(bar_e[j]);
-        }
-        return true;
-      }
-      // ---- S = K Q^T (16 keys x 8 heads per group), two accumulator chains each ----
-      float S[NG][4];
-#pragma unroll
-      for (int j = 0; j < NG; ++j) {
-        float Sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        const uint32_t row_g = sk[j] + (16 * gi + g) * k_key_stride + kvh * k_head_stride;
-        const uint32_t row_h = row_g + 8 * k_key_stride;
+      const int c = (int)lds32(sid0 + 4 * slot);
+      if (c < 0) break;   // the CTA's slots have run out
+#ifdef RD_TIMING_SWITCHES
+      if (i == 0) tr[3] = clock64();
+#endif
+      const uint32_t sk = my_ring + d * slot_sz, sv = sk + v_slot_off;
+      const int kfirst = key0 + c * kSlotKeys;  // first key of the slot
+#ifdef RD_TIMING_SWITCHES
+      if (!(p.debug & 1)) {
+#endif
+      // ---- S = K Q^T (16 keys x 8 heads), two accumulator chains ----
+      float Sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const uint32_t row_g = sk + k_row_off;
+        const uint32_t row_h = row_g + 8 * pitch_k;
+#ifdef RD_TIMING_SWITCHES
         if (!(p.debug & 4))
+#endif
         KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
           mma16816(Sc[n & 1], a0, a1, a2, a3, qb[n][0], qb[n][1]);
         });
-#pragma unroll
-        for (int i = 0; i < 4; ++i) S[j][i] = Sc[0][i] + Sc[1][i];
-        if (kbase[j] + 15 > t_last) {  // tail tile: keys beyond the last attended one
-          if (kbase[j] + g > t_last) S[j][0] = S[j][1] = -INFINITY;
-          if (kbase[j] + g + 8 > t_last) S[j][2] = S[j][3] = -INFINITY;
-        }
       }
-
-      uint32_t pb[NG][2];
-      if (p.debug & 16) {
+      float Sv[4];
 #pragma unroll
-        for (int j = 0; j < NG; ++j) pb[j][0] = pb[j][1] = __float_as_uint(S[j][0]) | 0x3c003c00u;
-      } else {
+      for (int j = 0; j < 4; ++j) Sv[j] = Sc[0][j] + Sc[1][j];
+      if (kfirst + 15 > t_last) {  // tail slot: keys beyond the last attended one
+        if (kfirst + g > t_last) Sv[0] = Sv[1] = -INFINITY;
+        if (kfirst + g + 8 > t_last) Sv[2] = Sv[3] = -INFINITY;
+      }
       // ---- online softmax (per head: columns 2t and 2t+1 of this lane) ----
-      float mx0 = fmaxf(S[0][0], S[0][2]), mx1 = fmaxf(S[0][1], S[0][3]);
+      run0 = fmaxf(run0, fmaxf(Sv[0], Sv[2]));
+      run1 = fmaxf(run1, fmaxf(Sv[1], Sv[3]));
+      if (__any_sync(FULL, run0 > m0 + kRefSlack || run1 > m1 + kRefSlack)) {
+        // move the references to the current maxima of the columns (over the 8 row lanes)
+        float n0 = run0, n1 = run1;
 #pragma unroll
-      for (int j = 1; j < NG; ++j) {
-        mx0 = fmaxf(mx0, fmaxf(S[j][0], S[j][2]));
-        mx1 = fmaxf(mx1, fmaxf(S[j][1], S[j][3]));
-      }
-#pragma unroll
-      for (int o = 4; o < 32; o <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, o));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, o));
-      }
-      if (__any_sync(FULL, mx0 > m0 || mx1 > m1)) {
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        for (int o = 4; o < 32; o <<= 1) {
+          n0 = fmaxf(n0, __shfl_xor_sync(FULL, n0, o));
+          n1 = fmaxf(n1, __shfl_xor_sync(FULL, n1, o));
+        }
+        n0 = fmaxf(n0, m0);
+        n1 = fmaxf(n1, m1);
         const float c0 = ex2(m0 - n0), c1 = ex2(m1 - n1);
         m0 = n0;
         m1 = n1;
         l0 *= c0;
         l1 *= c1;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          O[i][0] *= c0;
-          O[i][1] *= c1;
-          O[i][2] *= c0;
-          O[i][3] *= c1;
+        for (int j = 0; j < 16; ++j) {
+          O[j][0] *= c0;
+          O[j][1] *= c1;
+          O[j][2] *= c0;
+          O[j][3] *= c1;
         }
       }
-#pragma unroll
-      for (int j = 0; j < NG; ++j) {
-        const float p0 = ex2(S[j][0] - m0), p1 = ex2(S[j][1] - m1);
-        const float p2 = ex2(S[j][2] - m0), p3 = ex2(S[j][3] - m1);
-        l0 += p0 + p2;
-        l1 += p1 + p3;
-        // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
-        pb[j][0] = movmatrix_trans(pack_h2(p0, p1));
-        pb[j][1] = movmatrix_trans(pack_h2(p2, p3));
-      }
-      }
-
+      const float p0 = ex2(Sv[0] - m0), p1 = ex2(Sv[1] - m1);
+      const float p2 = ex2(Sv[2] - m0), p3 = ex2(Sv[3] - m1);
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
+      const uint32_t pb0 = movmatrix_trans(pack_h2(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(pack_h2(p2, p3));
       // ---- O^T += V^T P^T (256 dims x 8 heads) ----
-#pragma unroll
-      for (int j = 0; j < NG; ++j) {
+      {
         uint32_t rows[4];
-        const uint32_t r0 = sv[j] + (16 * gi + 2 * tq) * v_key_stride + kvh * v_head_stride;
+        const uint32_t r0 = sv + v_row_off;
         rows[0] = r0;
-        rows[1] = r0 + v_key_stride;
-        rows[2] = r0 + 8 * v_key_stride;
-        rows[3] = r0 + 9 * v_key_stride;
+        rows[1] = r0 + pitch_v;
+        rows[2] = r0 + 8 * pitch_v;
+        rows[3] = r0 + 9 * pitch_v;
+#ifdef RD_TIMING_SWITCHES
         if (!(p.debug & 8))
+#endif
         VL::run(rows, g, [&](int m, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-          mma16816(O[m], a0, a1, a2, a3, pb[j][0], pb[j][1]);
+          mma16816(O[m], a0, a1, a2, a3, pb0, pb1);
         });
       }
-      __syncwarp();
-      if (lane == 0) {
-#pragma unroll
-        for (int j = 0; j < NG; ++j) mbar_arrive(bar_e[j]);
+#ifdef RD_TIMING_SWITCHES
       }
-      return true;
-    };
-    {
-      int it = 0;
-      bool ok = true;
-      if (KG < 3 && p.stages >= 2)  // two tiles per step only where registers allow
-        for (; ok && it + 1 < ntiles; it += 2) ok = step(std::integral_constant<int, 2>(), it);
-      for (; ok && it < ntiles; ++it) ok = step(std::integral_constant<int, 1>(), it);
-      if (!ok) s_abort = 1;
+#endif
+      // ---- hand the slot back; the last of the group's warps refills it ----
+      __syncwarp();
+      uint32_t last = 0;
+      if (lane == 0) last = atom_add_acq_rel_shared(cnt0 + 4 * slot, 1u) == (uint32_t)(nkv - 1);
+      last = __shfl_sync(FULL, last, 0);
+      if (last) {
+        if (lane == 0) sts32(cnt0 + 4 * slot, 0u);
+        fill(gi, d);
+      }
+      if (++d == D) {
+        d = 0;
+        ph ^= 1;
+      }
     }
-    // row sums: add the 8 key-row lanes of each head column
+    RD_TRACE(4);
+    // row sums and true maxima: over the 8 key-row lanes of each head column
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
       l0 += __shfl_xor_sync(FULL, l0, o);
       l1 += __shfl_xor_sync(FULL, l1, o);
+      run0 = fmaxf(run0, __shfl_xor_sync(FULL, run0, o));
+      run1 = fmaxf(run1, __shfl_xor_sync(FULL, run1, o));
     }
-    if (VL::kUnscale != 1.0f) {
+    if (g == 0) {
+      const int c = kvh * 8 + 2 * tq;
+      s_m[gi][c] = m0, s_m[gi][c + 1] = m1;
+      s_t[gi][c] = run0, s_t[gi][c + 1] = run1;
+      s_l[gi][c] = l0, s_l[gi][c + 1] = l1;
+    }
+    // Park the accumulators (still relative to this warp's references) in the group's
+    // plane [head][dim], which lies over the group's own ring: the group's warps meet
+    // first, so nobody still reads a slot. Dim d of a head sits at 33 * (d >> 5) +
+    // (d & 31) and heads are kPlaneHead floats apart, which spreads the 8 row lanes (32
+    // dims apart for the block loaders) and the quad lanes (two heads apart) over
+    // different banks.
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(nkv * 32) : "memory");
+    if (!*(volatile int *)&s_abort && tq < kGroup / 2) {
+      float *plane = reinterpret_cast<float *>(smem + kRingOffset + (size_t)gi * group_bytes) +
+                     (kvh * kGroup + 2 * tq) * kPlaneHead;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        O[i][0] *= VL::kUnscale;
-        O[i][1] *= VL::kUnscale;
-        O[i][2] *= VL::kUnscale;
-        O[i][3] *= VL::kUnscale;
-      }
-    }
-  } else if (warp < CW) {
-    // consumer warp without a (kv head, group) item: only keeps the ring moving
-    int st = 0;
-    uint32_t ph = 0;
-    for (int it = 0; it < ntiles; ++it) {
-      if (!mbar_wait(bar_full + 8 * st, ph, p.status, 3)) {
-        s_abort = 1;
-        break;
-      }
-      if (lane == 0) mbar_arrive(bar_empty + 8 * st);
-      if (++st == p.stages) {
-        st = 0;
-        ph ^= 1;
+      for (int m = 0; m < 16; ++m) {
+        const int d0 = VL::dim(g, m, 0), d1 = VL::dim(g, m, 1);
+        const int a0 = 33 * (d0 >> 5) + (d0 & 31), a1 = 33 * (d1 >> 5) + (d1 & 31);
+        plane[a0] = O[m][0];
+        plane[a0 + kPlaneHead] = O[m][1];
+        plane[a1] = O[m][2];
+        plane[a1 + kPlaneHead] = O[m][3];
       }
     }
   }
 
   // ---- combine the key groups of each kv head and write one record per head ----
-  __syncthreads();  // every stage has been consumed (or the CTA is unwinding)
-  if (s_abort) {
+  __syncthreads();  // every slot has been consumed (or the CTA is unwinding)
+  RD_TRACE(5);
+  const bool aborted = s_abort != 0;
+  if (aborted) {
     // Unwinding after a bounded wait ran out: give copies still in flight one more
     // bounded chance to land before the CTA (and its shared memory) goes away.
     if (threadIdx.x == 0) {
-      for (int i = 0; i < p.stages && i < ntiles; ++i) {
-        const int laps = (ntiles - 1 - i) / p.stages;  // last tile that used stage i
-        mbar_wait(bar_full + 8 * i, laps & 1, nullptr, 0);
+      for (int i = 0; i < G * D; ++i) {
+        const uint32_t nf = lds32(nfill0 + 4 * i);
+        if (nf > 0) mbar_wait(bar_full + 8 * i, (nf - 1) & 1, nullptr, 0);
       }
     }
     __syncthreads();
   }
-  // Staging (aliases the tile ring): [warp][head][m, l, 8 blocks x 33 floats]; dim d of
-  // a head sits at 2 + 33*(d >> 5) + (d & 31), so the 8 row-lanes of a fragment (32 dims
-  // apart for the block loaders) hit 8 different banks.
-  float *stg = reinterpret_cast<float *>(smem + kRingOffset);
-  __shared__ float s_wgt[3][4 * kGroup];
-  if (p.debug & 64) return;
-  if (active) {
-    float *mine = stg + (size_t)warp * kStgWarp;
+  {
+    const size_t head_stride = (size_t)S * kRec;
+    const bool wide = (reinterpret_cast<uintptr_t>(rec0) & 7) == 0;  // always true for the library's workspace
+    const float *planes = reinterpret_cast<const float *>(smem + kRingOffset);
+    const size_t plane_stride = group_bytes / sizeof(float);
+    for (int idx = threadIdx.x; idx < nkv * kGroup * (kHeadDim / 2); idx += NT) {
+      const int h = idx >> 7, dd = 2 * (idx & 127);
+      const int c = (h / kGroup) * 8 + h % kGroup;
+      float mm = kNegBig;
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int head = 2 * tq + hh;
-      if (head < kGroup) {
-        float *rec = mine + head * kStgHead;
-        if (g == 0) {
-          const float mh = hh ? m1 : m0;
-          rec[0] = mh <= 0.5f * kNegBig ? -INFINITY : mh;  // no key seen: the empty record
-          rec[1] = hh ? l1 : l0;
-        }
+      for (int w = 0; w < G; ++w) mm = fmaxf(mm, s_t[w][c]);
+      const bool empty = aborted || mm <= 0.5f * kNegBig;
+      const int off = h * kPlaneHead + 33 * (dd >> 5) + (dd & 31);
+      float a0 = 0.f, a1 = 0.f, ll = 0.f;
 #pragma unroll
-        for (int m = 0; m < 16; ++m) {
-          const int d0 = VL::dim(g, m, 0), d1 = VL::dim(g, m, 1);
-          rec[2 + 33 * (d0 >> 5) + (d0 & 31)] = O[m][hh];
-          rec[2 + 33 * (d1 >> 5) + (d1 & 31)] = O[m][2 + hh];
+      for (int w = 0; w < G; ++w) {
+        const float wg = ex2(s_m[w][c] - mm);   // references never exceed the true maximum
+        ll += s_l[w][c] * wg;
+        if (!empty) {
+          a0 += planes[w * plane_stride + off] * wg;
+          a1 += planes[w * plane_stride + off + 1] * wg;
         }
+      }
+      a0 *= VL::kUnscale;
+      a1 *= VL::kUnscale;
+      float *rec = rec0 + h * head_stride;
+      if (dd == 0) {
+        rec[0] = empty ? -INFINITY : mm * 0.6931471805599453f;  // natural log
+        rec[1] = empty ? 0.f : ll;
+      }
+      if (wide) {
+        *reinterpret_cast<float2 *>(rec + 2 + dd) = make_float2(a0, a1);
+      } else {
+        rec[2 + dd] = a0;
+        rec[3 + dd] = a1;
       }
     }
   }
-  __syncthreads();
-  const int n_heads_cta = nkv * kGroup;
-  if ((int)threadIdx.x < n_heads_cta) {
-    // per head: weights of its key groups, and the record header
-    const int h = threadIdx.x, hk = h / kGroup, hh = h % kGroup;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < KG; ++w) mm = fmaxf(mm, stg[(w * nkv + hk) * kStgWarp + hh * kStgHead]);
-    float ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < KG; ++w) {
-      const float *rec = stg + (w * nkv + hk) * kStgWarp + hh * kStgHead;
-      const float wgt = (mm == -INFINITY || s_abort) ? 0.f : ex2(rec[0] - mm);
-      s_wgt[w][h] = wgt;
-      ll += rec[1] * wgt;
-    }
-    float *out = rec0 + (size_t)h * S * kRec;
-    out[0] = (mm == -INFINITY || s_abort) ? -INFINITY : mm * 0.6931471805599453f;  // natural log
-    out[1] = ll;
-  }
-  __syncthreads();
-  const size_t head_stride = (size_t)S * kRec;
-  if ((reinterpret_cast<uintptr_t>(rec0) & 7) == 0) {
-    // records are 8-byte aligned (always true for the library's own workspace): two dims
-    // per thread and store
-#pragma unroll 2
-    for (int idx = threadIdx.x; idx < n_heads_cta * (kHeadDim / 2); idx += blockDim.x) {
-      const int h = idx >> 7, d = 2 * (idx & 127);
-      const int hk = h / kGroup, hh = h % kGroup;
-      const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int w = 0; w < KG; ++w) {
-        const float wg = s_wgt[w][h];
-        a0 += stg[(w * nkv + hk) * kStgWarp + off] * wg;
-        a1 += stg[(w * nkv + hk) * kStgWarp + off + 1] * wg;
-      }
-      *reinterpret_cast<float2 *>(rec0 + h * head_stride + 2 + d) = make_float2(a0, a1);
-    }
-  } else {
-    for (int idx = threadIdx.x; idx < n_heads_cta * kHeadDim; idx += blockDim.x) {
-      const int h = idx >> 8, d = idx & 255;
-      const int hk = h / kGroup, hh = h % kGroup;
-      const int off = hh * kStgHead + 2 + 33 * (d >> 5) + (d & 31);
-      float acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < KG; ++w) acc += stg[(w * nkv + hk) * kStgWarp + off] * s_wgt[w][h];
-      rec0[h * head_stride + 2 + d] = acc;
+#ifdef RD_TIMING_SWITCHES
+  if (p.debug & 32) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      RD_TRACE(6);
+      unsigned *o = reinterpret_cast<unsigned *>(rec0 + 2);
+      o[0] = (unsigned)gt0;
+      for (int i = 1; i < 7; ++i) o[i] = (unsigned)(tr[i] - tr[0]);
+      o[7] = (unsigned)n_slots;
     }
   }
+#endif
 }
+#undef RD_TRACE
 
 // Shared-memory plan of one (KT, VT) instantiation and the opt-in for it.
 template <int KT, int VT, bool MULTI>
-int prepare_decode(int n_head_kv, int *stages_out, size_t *smem_out) {
-  constexpr int KG = key_groups(KT, VT);
-  constexpr int TILE = 16 * KG;
-  const int pitch = key_pitch(KT, n_head_kv) + key_pitch(VT, n_head_kv);
-  const int stage_bytes = TILE * pitch;
-  int stages = (kSmemBudget - kRingOffset) / stage_bytes;
-  if (stages < 1) return RD_ERR_UNSUPPORTED;
-  if (stages > kMaxStages) stages = kMaxStages;
-  size_t smem = kRingOffset + (size_t)stages * stage_bytes;
-  const size_t merge_bytes = kRingOffset + (size_t)4 * KG * kStgWarp * sizeof(float);
-  if (smem < merge_bytes) smem = merge_bytes;
+int prepare_decode(int n_head_kv, int *depth_out, int *group_bytes_out, size_t *smem_out) {
+  constexpr int G = key_groups(KT, VT);
+  const int depth = ring_depth(KT, VT, n_head_kv);
+  if (depth < 1) return RD_ERR_UNSUPPORTED;
+  // a group's ring doubles as its epilogue plane [head][kPlaneHead] of f32
+  size_t group_bytes = (size_t)depth * slot_bytes(KT, VT, n_head_kv);
+  const size_t plane_bytes = (size_t)n_head_kv * kGroup * kPlaneHead * sizeof(float);
+  if (group_bytes < plane_bytes) group_bytes = (plane_bytes + 127) & ~(size_t)127;
+  const size_t smem = kRingOffset + (size_t)G * group_bytes;
+  if (smem > (size_t)kSmemBudget) return RD_ERR_UNSUPPORTED;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;
@@ -1052,37 +1109,39 @@ int prepare_decode(int n_head_kv, int *stages_out, size_t *smem_out) {
       return RD_ERR_CUDA;
     if (dev >= 0 && dev < 8) attr_set[dev] = true;
   }
-  *stages_out = stages;
+  *depth_out = depth;
+  *group_bytes_out = (int)group_bytes;
   *smem_out = smem;
   return RD_OK;
 }
 
+#ifdef RD_TIMING_SWITCHES
 inline int decode_debug_mask() {
   const char *e = getenv("RD_DECODE_DEBUG");
   return e ? atoi(e) : 0;
 }
+#endif
 
 // Host side of one (KT, VT) instantiation.
 template <int KT, int VT>
 int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
-  constexpr int KG = key_groups(KT, VT);
-  constexpr int TILE = 16 * KG;
-  int stages = 0;
+  constexpr int G = key_groups(KT, VT);
+  int depth = 0, group_bytes = 0;
   size_t smem = 0;
-  const int rc = prepare_decode<KT, VT, false>(a.n_head_kv, &stages, &smem);
+  const int rc = prepare_decode<KT, VT, false>(a.n_head_kv, &depth, &group_bytes, &smem);
   if (rc != RD_OK) return rc;
   DecodeKernelArgs k;
   memset(&k, 0, sizeof(k));
-  // Quantized keys are small (576 / 1088 bytes for 4 kv heads), so a whole tile comes in
+  // Quantized keys are small (576 / 1088 bytes for 4 kv heads), so a whole slot comes in
   // as one tensor-map copy; f16 / f32 keys are too wide for one box and large enough for
   // one plain bulk copy per key. Tensor maps need the key count on the host, so
   // launches that take it from a device array use bulk copies as well.
   const bool host_keys = a.pos == nullptr;
   const int64_t n_rows = (int64_t)a.t + 1;
   k.k_tmap = host_keys && n_rows > 0 && KT >= RD_KV_Q8_0 &&
-             encode_kv_tmap(&k.tm_k, a.k, KT, a.n_head_kv, n_rows, TILE) == RD_OK;
+             encode_kv_tmap(&k.tm_k, a.k, KT, a.n_head_kv, n_rows, kSlotKeys) == RD_OK;
   k.v_tmap = host_keys && n_rows > 0 && VT >= RD_KV_Q8_0 &&
-             encode_kv_tmap(&k.tm_v, a.v, VT, a.n_head_kv, n_rows, TILE) == RD_OK;
+             encode_kv_tmap(&k.tm_v, a.v, VT, a.n_head_kv, n_rows, kSlotKeys) == RD_OK;
   k.q = a.q;
   k.k = (const uint8_t *)a.k;
   k.v = (const uint8_t *)a.v;
@@ -1093,15 +1152,17 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.n_head = a.n_head;
   k.nkv = a.n_head_kv;
   k.qscale = a.scale * 1.4426950408889634f;
-  k.stages = stages;
+  k.depth = depth;
+  k.group_bytes = group_bytes;
+#ifdef RD_TIMING_SWITCHES
   k.debug = decode_debug_mask();
+#endif
   k.status = a.status;
   k.k_new = a.k_new;
   k.v_new = a.v_new;
   k.new_row = a.new_row;
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
-  return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3((4 * KG + 1) * 32), smem, st, k) ==
-                 cudaSuccess
+  return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3(4 * G * 32), smem, st, k) == cudaSuccess
              ? RD_OK
              : RD_ERR_CUDA;
 }
@@ -1110,22 +1171,21 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
 // and launches one CTA per work item (launch).
 template <int KT, int VT>
 int multi_decode_typed(const MultiDecodeArgs &a, cudaStream_t st) {
-  constexpr int KG = key_groups(KT, VT);
-  constexpr int TILE = 16 * KG;
+  constexpr int G = key_groups(KT, VT);
   if (a.host_seqs != nullptr) {
     for (int i = 0; i < a.n_seq; ++i) {
       DecodeSeq &d = a.host_seqs[i];
       const int64_t n_rows = (int64_t)d.t + 1;
       d.k_tmap = n_rows > 0 && KT >= RD_KV_Q8_0 &&
-                 encode_kv_tmap(d.tm_k, d.k, KT, a.n_head_kv, n_rows, TILE) == RD_OK;
+                 encode_kv_tmap(d.tm_k, d.k, KT, a.n_head_kv, n_rows, kSlotKeys) == RD_OK;
       d.v_tmap = n_rows > 0 && VT >= RD_KV_Q8_0 &&
-                 encode_kv_tmap(d.tm_v, d.v, VT, a.n_head_kv, n_rows, TILE) == RD_OK;
+                 encode_kv_tmap(d.tm_v, d.v, VT, a.n_head_kv, n_rows, kSlotKeys) == RD_OK;
     }
     return RD_OK;
   }
-  int stages = 0;
+  int depth = 0, group_bytes = 0;
   size_t smem = 0;
-  const int rc = prepare_decode<KT, VT, true>(a.n_head_kv, &stages, &smem);
+  const int rc = prepare_decode<KT, VT, true>(a.n_head_kv, &depth, &group_bytes, &smem);
   if (rc != RD_OK) return rc;
   DecodeKernelArgs k;
   memset(&k, 0, sizeof(k));
@@ -1133,14 +1193,17 @@ int multi_decode_typed(const MultiDecodeArgs &a, cudaStream_t st) {
   k.n_head = a.n_head;
   k.nkv = a.n_head_kv;
   k.qscale = a.scale * 1.4426950408889634f;
-  k.stages = stages;
+  k.depth = depth;
+  k.group_bytes = group_bytes;
+#ifdef RD_TIMING_SWITCHES
   k.debug = decode_debug_mask();
+#endif
   k.status = a.status;
   k.seqs = a.dev_seqs;
   k.items = a.dev_items;
   k.q_len = a.q_len;
-  return launch_pdl(2, decode_kernel<KT, VT, true>, dim3((unsigned)a.n_items), dim3((4 * KG + 1) * 32),
-                    smem, st, k) == cudaSuccess
+  return launch_pdl(2, decode_kernel<KT, VT, true>, dim3((unsigned)a.n_items), dim3(4 * G * 32), smem, st,
+                    k) == cudaSuccess
              ? RD_OK
              : RD_ERR_CUDA;
 }
