@@ -112,12 +112,23 @@ def reference_arm(args):
     if rank != 0:
         return
     ora = Oracle()
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to every rank: ask for all host
+    # threads explicitly, so that the arm is the same at every N
+    ora.set_threads(os.cpu_count() or 1)
     cores = ora.num_threads()
     kc = ora.kv_fill(KT, N_KEYS * NKV, HD, 11)
     vc = ora.kv_fill(VT, N_KEYS * NKV, HD, 22)
     q = ora.kv_fill_values(NH, HD, 3)
-    steps, warm = max(1, min(args.steps, 3)), max(0, min(args.warmup, 1))
-    for _ in range(warm):
+    # --steps / --warmup are honoured as long as the whole arm stays within about a
+    # minute of CPU time (one step = one layer of the workload)
+    budget_s = 60.0
+    t0 = time.perf_counter()
+    ora.attn(q[None], kc, vc, [POS], NKV, SCALE, KT, VT)
+    one = time.perf_counter() - t0
+    afford = max(1, int(budget_s / max(one, 1e-6)))
+    warm = max(0, min(args.warmup, afford // 4))
+    steps = max(1, min(args.steps, afford - warm))
+    for _ in range(max(0, warm - 1)):     # the probe above was the first warm-up step
         ora.attn(q[None], kc, vc, [POS], NKV, SCALE, KT, VT)
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -567,14 +578,83 @@ def main():
     sampler = ClockSampler(local)
     g_dev, per_step = make_graph(False)
     g_e2e, _ = make_graph(True)
-    timed(g_dev, W, False)
+    rd.check(L.rd_device_status(), "device status after capture")
+
+    # Protocol of the reference's own attention bench (tests/bench_attn_gpu.hip:64-101,
+    # 1756-1768): at least 300 ms of warm-up, then interleaved rounds with mean and min.
+    # The contract's number comes first: W warm-up steps (more if 300 ms need more), then
+    # EXACTLY K timed steps -> value / e2e. After that ROUNDS further rounds of K steps of
+    # each graph, interleaved, give the mean and the best round.
+    def warm(gph, host_io):
+        done = timed(gph, W, host_io)
+        while done < 300.0:
+            done += timed(gph, max(W, 50), host_io)
+    warm(g_dev, False)
     sampler.start()
     ms_dev = timed(g_dev, K, False)
     n_launch = per_step * K
-    timed(g_e2e, min(W, 3), True)
+    warm(g_e2e, True)
     ms_e2e = timed(g_e2e, K, True)
+    ROUNDS = 10
+    r_dev, r_e2e = [], []
+    for _ in range(ROUNDS):
+        r_dev.append(timed(g_dev, K, False))
+        r_e2e.append(timed(g_e2e, K, True))
     clocks = sampler.stop()
     rd.check(L.rd_device_status(), "device status")
+
+    # ---- N > 1: is the sharded answer right? -----------------------------------------
+    # One more step through the timed path on fresh inputs, then every layer again through
+    # the plain route (per-rank records -> NCCL all-gather -> rd_attn_merge) and, on rank 0
+    # for layer 0, through the CPU oracle over the gathered cache slices. The run fails
+    # above the attention gate (max-abs 2e-3, cosine 0.9999).
+    parity = None
+    if world > 1:
+        in_dev.copy_(in_host)
+        one_step(False)
+        torch.cuda.synchronize()
+        o_fused = o_dev.clone()
+        in_dev.copy_(in_host)
+        o_chk = torch.empty_like(o_dev)
+        stp = rd.stream_ptr()
+        for l in range(n_layers):
+            rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
+                                         rd.ptr(rec_mine), 0, slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, 1,
+                                         None, rd.ptr(ws), ws_bytes, stp))
+            dist.all_gather_into_tensor(rec_all, rec_mine)
+            rec_merge.copy_(rec_all.view(world, NH, 2 + HD).transpose(0, 1))
+            rd.check(L.rd_attn_merge(rd.ptr(rec_merge), rd.ptr(o_chk[l]), NH, HD, world, rd.ptr(gate_dev[l]), stp))
+        torch.cuda.synchronize()
+        a, b = o_fused.double().flatten(), o_chk.double().flatten()
+        stats = torch.tensor([float((a - b).abs().max()),
+                              -float((a @ b) / ((a @ a).sqrt() * (b @ b).sqrt()).clamp_min(1e-300))], device="cuda")
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)       # worst rank: largest error, smallest cosine
+        parity = {"max_abs": float(stats[0]), "cosine": -float(stats[1]),
+                  "vs": "per-rank records -> NCCL all-gather -> rd_attn_merge, all layers, worst rank"}
+        # layer 0 against the CPU oracle: gather the cache slices on every rank (padded to the
+        # common slice length), rank 0 stitches them and recomputes the attention on the host
+        pad = per * NKV * row
+        def gathered(t):
+            mine = torch.zeros(pad, dtype=torch.uint8, device="cuda")
+            mine[:t.numel()] = t if slice_rows > 0 else t[:0]
+            allv = torch.empty(world * pad, dtype=torch.uint8, device="cuda")
+            dist.all_gather_into_tensor(allv, mine)
+            return allv[:N_KEYS * NKV * row].cpu().numpy()     # every slice but the last is full
+        kc0 = gathered(kcache[0][:slice_rows * NKV * row])
+        vc0 = gathered(vcache[0][:slice_rows * NKV * row])
+        if rank == 0:
+            from oracle.oracle import Oracle
+            ora = Oracle()
+            ora.set_threads(os.cpu_count() or 1)
+            q0 = in_host[0, :NH * HD].view(NH, HD).numpy()
+            g0 = in_host[0, NH * HD:2 * NH * HD].view(NH, HD).numpy()
+            y = ora.attn(q0[None], kc0, vc0, [POS], NKV, SCALE, KT, VT)[0]
+            _, want = ora.sigmoid_gate(g0.copy(), y)
+            got = o_fused[0].cpu().numpy().astype(np.float64)
+            want = np.asarray(want, dtype=np.float64)
+            parity["oracle_layer0_max_abs"] = float(np.abs(got - want).max())
+            parity["oracle_layer0_cosine"] = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
+        rd.check(L.rd_device_status(), "device status after the parity check")
     st = rd.stream_ptr()
 
     bytes_layer = algorithmic_bytes(N_KEYS, row, row)
@@ -619,10 +699,15 @@ def main():
     k_ms_min = min(rounds)
     k_bytes = algorithmic_bytes(slice_rows, row, row)
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
-    # dram__bytes_read + dram__bytes_write of one full-size launch (131001 keys), from the
-    # ncu capture summarised in profiles/decode_kernel_q4_0_131001keys.md; a context slice
-    # moves proportionally fewer bytes.
-    traffic = (151.00e6 + 7.82e6) * slice_rows / N_KEYS
+    # DRAM bytes of one full-size launch (131001 keys) as captured with ncu; the figures
+    # live in a small json beside the capture's summary. A context slice moves
+    # proportionally fewer bytes. None when the file is missing.
+    traffic = None
+    try:
+        cap = json.load(open(os.path.join(ROOT, "profiles", "decode_kernel_q4_0_131001keys.json")))
+        traffic = (cap["dram_bytes_read"] + cap["dram_bytes_write"]) * slice_rows / cap["n_keys"]
+    except Exception:
+        pass
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "decode_kernel<q4_0,q4_0>", "kernel_us": k_ms * 1e3, "kernel_us_min_round": k_ms_min * 1e3,
                 "peak_source": peak_src, "frac_of_8tbs_nominal": achieved / 8000.0}
@@ -636,6 +721,11 @@ def main():
                 "h2d_bytes_per_step": in_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4},
         "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
         "us_per_layer": ms_dev / K / n_layers * 1e3,
+        "rounds": {"n": ROUNDS, "steps_each": K, "warmup_ms_min": 300,
+                   "value_mean": bytes_step * K * ROUNDS / (sum(r_dev) * 1e-3) / 1e9,
+                   "value_best": bytes_step * K / (min(r_dev) * 1e-3) / 1e9,
+                   "e2e_mean": bytes_step * K * ROUNDS / (sum(r_e2e) * 1e-3) / 1e9,
+                   "e2e_best": bytes_step * K / (min(r_e2e) * 1e-3) / 1e9},
     }
     out["config"]["exchange"] = exchange
     if rank == 0 and world == 1 and args.leg == "all":
@@ -662,20 +752,32 @@ def main():
                                "cores": ora.num_threads(), "kind": "port",
                                "sample": f"{n_cpu} layer-steps (131001 keys each) of the same workload, "
                                "CPU oracle f32 attention, OpenMP over heads", "seconds": dt}
+    if parity is not None:
+        out["parity_check"] = parity
     if saved_stdout is not None:
         sys.stdout.flush()
         os.dup2(saved_stdout, 1)
     if rank == 0:
         print(json.dumps(out), flush=True)
+    bad = parity is not None and (parity["max_abs"] > 2e-3 or parity["cosine"] < 0.9999 or
+                                  parity.get("oracle_layer0_max_abs", 0.0) > 2e-3 or
+                                  parity.get("oracle_layer0_cosine", 1.0) < 0.9999)
     if world > 1:
-        # Leave without tearing NCCL down: destroying a process group whose collectives
-        # were captured in CUDA graphs has been seen to block at exit. Everything is
-        # already synchronised and printed, so a hard exit loses nothing.
+        # Orderly teardown: the graphs (which may hold captured collectives and the
+        # symmetric-memory buffers) go first, then the process group. A watchdog ends the
+        # process should the teardown block; everything is synchronised and printed by then.
         torch.cuda.synchronize()
         dist.barrier()
+        code = 3 if bad else 0
+        threading.Timer(30.0, lambda: os._exit(code)).start()
+        del g_dev, g_e2e, kg
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(code)     # the watchdog thread must not keep the interpreter alive
+    if bad:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

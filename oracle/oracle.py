@@ -33,11 +33,18 @@ def _f32(a):
     return a
 
 
+def reference_dir() -> str | None:
+    """The reference checkout: $RD_REFERENCE_DIR, else a directory named `reference` beside
+    this repository; None where neither holds the headers."""
+    cand = os.environ.get("RD_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "include", "rdna4")) else None
+
+
 def build(ref: bool = True) -> None:
     """Compile the checker libraries (the reference one only if its checkout is there)."""
     subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
-    if ref and os.path.isdir("/root/reference/include/rdna4"):
-        subprocess.check_call(["make", "-s", "-C", HERE, "ref"])
+    if ref and reference_dir() is not None:
+        subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + reference_dir()])
 
 
 class _AttnMixin:

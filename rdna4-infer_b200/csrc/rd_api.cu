@@ -39,13 +39,17 @@ int sm_count(int dev) {
   return g_dev[dev].sms;
 }
 
-// Lazily allocated status word (only the allocating entry points create it).
-DeviceStatus *status_word(int dev, bool create) {
+// Status word of the bounded waits: part of the library image (zero-initialised when the
+// module is loaded on a device), so every entry point has one without allocating -- also
+// under stream capture and on a process's very first call. In host code the symbol's name
+// is only a stand-in; its device address is looked up once per device.
+static __device__ __align__(256) DeviceStatus g_status_word;
+
+DeviceStatus *status_word(int dev) {
   std::lock_guard<std::mutex> lk(g_mu);
-  if (g_dev[dev].status == nullptr && create) {
+  if (g_dev[dev].status == nullptr) {
     void *p = nullptr;
-    if (cudaMalloc(&p, 256) == cudaSuccess && cudaMemset(p, 0, 256) == cudaSuccess)
-      g_dev[dev].status = (DeviceStatus *)p;
+    if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) g_dev[dev].status = (DeviceStatus *)p;
   }
   return g_dev[dev].status;
 }
@@ -158,6 +162,8 @@ int attn_alloc(const float *q, const void *k, const void *v, float *out, float *
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   const int sms = sm_count(dev);
   size_t bytes = workspace_bytes_for(sms, n_tok, n_head);
   if (out == nullptr) {
@@ -167,7 +173,7 @@ int attn_alloc(const float *q, const void *k, const void *v, float *out, float *
   void *ws = ensure_workspace(dev, bytes);
   if (ws == nullptr) return RD_ERR_WORKSPACE;
   return attn_core(q, k, v, out, records, n_rec, pos, t, 0, n_tok, n_head, n_head_kv, scale, kt, vt,
-                   nullptr, ws, bytes, status_word(dev, true), sms, (cudaStream_t)stream);
+                   nullptr, ws, bytes, status, sms, (cudaStream_t)stream);
 }
 
 // ---- allocation-free decode (rd_attn_decode_noalloc) --------------------------------
@@ -430,8 +436,10 @@ int rd_attn_decode_ws(const float *q, const void *k, const void *v, float *out, 
   if (!aligned(k, 16) || !aligned(v, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   return attn_core(q, k, v, out, partial, n_splits, nullptr, t, key_begin, 1, n_head, n_head_kv,
-                   scale, k_type, v_type, gate, workspace, workspace_bytes, status_word(dev, false),
+                   scale, k_type, v_type, gate, workspace, workspace_bytes, status,
                    sm_count(dev), (cudaStream_t)stream);
 }
 
@@ -452,6 +460,8 @@ int rd_attn_decode_append_ws(const float *q, const float *k_new, const float *v_
   if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   // keys 0..t-1 through the split-KV kernel (whose first CTAs also store row t), then the
   // merge with row t folded in
   const int tile = decode_tile_keys(k_type, v_type);
@@ -471,7 +481,7 @@ int rd_attn_decode_append_ws(const float *q, const float *k_new, const float *v_
   a.n_head_kv = n_head_kv;
   a.scale = scale;
   a.n_splits = S;
-  a.status = status_word(dev, false);
+  a.status = status;
   a.k_new = k_new;
   a.v_new = v_new;
   a.new_row = t;
@@ -499,6 +509,8 @@ int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   float *records = noalloc_records(dev);  // first call on this device: address look-up
   if (records == nullptr) return RD_ERR_CUDA;
   // Planning with at most RD_NOALLOC_MAX_SPLITS "SMs" caps the records per head, so the
@@ -506,7 +518,7 @@ int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *
   int sms = sm_count(dev);
   if (sms > RD_NOALLOC_MAX_SPLITS) sms = RD_NOALLOC_MAX_SPLITS;
   return attn_core(q, k, v, out, nullptr, 1, nullptr, t, 0, 1, n_head, n_head_kv, scale, k_type,
-                   v_type, gate, records, kNoAllocFloats * sizeof(float), status_word(dev, false),
+                   v_type, gate, records, kNoAllocFloats * sizeof(float), status,
                    sms, (cudaStream_t)stream);
 }
 
@@ -544,6 +556,8 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
   }
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   const int sms = sm_count(dev);
   const int max_items = multi_max_items(sms, n_seq, q_len);
   const size_t off_items = align256((size_t)n_seq * sizeof(DecodeSeq));
@@ -610,7 +624,7 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
   a.n_head = n_head;
   a.scale = scale;
   a.records = reinterpret_cast<float *>((unsigned char *)workspace + off_rec);
-  a.status = status_word(dev, false);
+  a.status = status;
   if ((rc = launch_decode_multi(k_type, v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
   return launch_merge_multi(a.dev_seqs, a.records, n_seq, q_len, n_head, (cudaStream_t)stream);
 }
@@ -666,7 +680,9 @@ int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,
   if (rc != RD_OK) return rc;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
-  return launch_shard_merge(out, gate, n_head, g, status_word(dev, true), (cudaStream_t)stream);
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
+  return launch_shard_merge(out, gate, n_head, g, status, (cudaStream_t)stream);
 }
 
 int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *out, int t,
@@ -684,11 +700,12 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
   if (!aligned(k, 16) || !aligned(v, 16) || !aligned(workspace, 256)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   const int tile = decode_tile_keys(k_type, v_type);
   const int64_t tiles = ((int64_t)t + tile) / tile;  // ceil((t + 1) / tile); 0 for an empty slice
   const int S = plan_splits(sm_count(dev), 1, tiles);
   if (workspace_bytes < partial_floats(1, n_head, S) * sizeof(float)) return RD_ERR_WORKSPACE;
-  DeviceStatus *status = status_word(dev, true);
   DecodeArgs a;
   a.q = q;
   a.k = k;
@@ -755,8 +772,10 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
   return launch_prefill(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, scale, n_rot,
-                        freq_base, status_word(dev, false), (cudaStream_t)stream);
+                        freq_base, status, (cudaStream_t)stream);
 }
 
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
@@ -778,7 +797,7 @@ int rd_device_status(void) {
   int dev;
   int rc = current_device(&dev);
   if (rc != RD_OK) return rc;
-  DeviceStatus *st = status_word(dev, true);
+  DeviceStatus *st = status_word(dev);
   if (st == nullptr) return RD_ERR_CUDA;
   if (cudaDeviceSynchronize() != cudaSuccess) return RD_ERR_CUDA;
   DeviceStatus h;

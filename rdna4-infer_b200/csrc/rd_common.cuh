@@ -57,6 +57,7 @@ struct DeviceStatus {
 // streams 16-key slots through its own ring of D shared-memory slots.
 constexpr int kMaxStages = 8;            // ring depth per key group
 constexpr int kMaxGroups = 3;
+constexpr int kMaxPos = 24;              // ring positions of a CTA, all groups together
 constexpr int kSmemBudget = 225 * 1024;  // dynamic, per CTA, of the 227 KB an sm_100 CTA may use
 constexpr int kSlotKeys = 16;            // keys per ring slot = rows of one MMA tile
 
@@ -88,7 +89,8 @@ __host__ __device__ constexpr int key_groups(int kt, int vt) {
 // Ring depth per group for n_head_kv kv heads (0: one slot does not fit).
 __host__ __device__ constexpr int ring_depth(int kt, int vt, int nkv) {
   const int d = (kSmemBudget - kRingOffset) / (key_groups(kt, vt) * slot_bytes(kt, vt, nkv));
-  return d > kMaxStages ? kMaxStages : d;
+  const int cap = kMaxPos / key_groups(kt, vt) < kMaxStages ? kMaxPos / key_groups(kt, vt) : kMaxStages;
+  return d > cap ? cap : d;
 }
 
 // ---- programmatic dependent launch ---------------------------------------------
@@ -104,11 +106,15 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 inline int pdl_mask() {
+#ifdef RD_TIMING_SWITCHES
   static const int m = [] {
     const char *e = getenv("RD_PDL");
-    return e ? atoi(e) : 2;   // measured: only the decode kernel gains as a dependent launch
+    return e ? atoi(e) : 2;
   }();
   return m;
+#else
+  return 2;   // measured: only the decode kernel gains as a dependent launch
+#endif
 }
 template <class... KArgs, class... Args>
 inline cudaError_t launch_pdl(int which, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -657,9 +657,9 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   // the query fragments; then the rings, group
   // after group (p.group_bytes apart: a group's ring also holds its epilogue plane).
   const uint32_t bar_full = smem_u32(smem);                       // 24 x 8 bytes
-  const uint32_t cnt0 = bar_full + 8 * kMaxGroups * kMaxStages;   // 24 x 4 bytes
-  const uint32_t nfill0 = cnt0 + 4 * kMaxGroups * kMaxStages;     // 24 x 4 bytes
-  const uint32_t sid0 = nfill0 + 4 * kMaxGroups * kMaxStages;     // 24 x 4 bytes: slot held, or -1
+  const uint32_t cnt0 = bar_full + 8 * kMaxPos;   // 24 x 4 bytes
+  const uint32_t nfill0 = cnt0 + 4 * kMaxPos;     // 24 x 4 bytes
+  const uint32_t sid0 = nfill0 + 4 * kMaxPos;     // 24 x 4 bytes: slot held, or -1
   uint8_t *qstage = smem + kBarBytes;
   const uint32_t ring0 = bar_full + kRingOffset;                  // 128-byte aligned
   const uint32_t group_bytes = (uint32_t)p.group_bytes;
@@ -880,28 +880,20 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
     const uint32_t my_ring = ring0 + gi * group_bytes;
     const uint32_t k_row_off = (uint32_t)g * pitch_k + kvh * RK;
     const uint32_t v_row_off = (uint32_t)(2 * tq) * pitch_v + kvh * RV;
-    int d = 0;         // ring position of the next slot to consume
-    uint32_t ph = 0;   // and the parity its full barrier completes with
-    for (int i = 0;; ++i) {
-      const int slot = gi * D + d;
-      if (!mbar_wait(bar_full + 8 * slot, ph, p.status, 2)) {
-        s_abort = 1;
-        break;
-      }
-      const int c = (int)lds32(sid0 + 4 * slot);
-      if (c < 0) break;   // the CTA's slots have run out
-#ifdef RD_TIMING_SWITCHES
-      if (i == 0) tr[3] = clock64();
-#endif
-      const uint32_t sk = my_ring + d * slot_sz, sv = sk + v_slot_off;
-      const int kfirst = key0 + c * kSlotKeys;  // first key of the slot
+    // One step consumes NS consecutive ring positions (pos[j], holding slot cs[j]). Two
+    // per step give the scheduler two independent dequantize -> MMA streams per warp and
+    // halve the softmax and hand-back bookkeeping.
+    auto step = [&](auto nsc, const int (&pos)[2], const int (&dd)[2], const int (&cs)[2]) {
+      constexpr int NS = decltype(nsc)::value;
 #ifdef RD_TIMING_SWITCHES
       if (!(p.debug & 1)) {
 #endif
-      // ---- S = K Q^T (16 keys x 8 heads), two accumulator chains ----
-      float Sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      {
-        const uint32_t row_g = sk + k_row_off;
+      // ---- S = K Q^T (16 keys x 8 heads per slot), two accumulator chains each ----
+      float Sv[NS][4];
+#pragma unroll
+      for (int j = 0; j < NS; ++j) {
+        float Sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const uint32_t row_g = my_ring + dd[j] * slot_sz + k_row_off;
         const uint32_t row_h = row_g + 8 * pitch_k;
 #ifdef RD_TIMING_SWITCHES
         if (!(p.debug & 4))
@@ -909,17 +901,17 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
         KL::run(row_g, row_h, tq, [&](int n, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
           mma16816(Sc[n & 1], a0, a1, a2, a3, qb[n][0], qb[n][1]);
         });
-      }
-      float Sv[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) Sv[j] = Sc[0][j] + Sc[1][j];
-      if (kfirst + 15 > t_last) {  // tail slot: keys beyond the last attended one
-        if (kfirst + g > t_last) Sv[0] = Sv[1] = -INFINITY;
-        if (kfirst + g + 8 > t_last) Sv[2] = Sv[3] = -INFINITY;
+        for (int e = 0; e < 4; ++e) Sv[j][e] = Sc[0][e] + Sc[1][e];
+        const int kfirst = key0 + cs[j] * kSlotKeys;  // first key of the slot
+        if (kfirst + 15 > t_last) {  // tail slot: keys beyond the last attended one
+          if (kfirst + g > t_last) Sv[j][0] = Sv[j][1] = -INFINITY;
+          if (kfirst + g + 8 > t_last) Sv[j][2] = Sv[j][3] = -INFINITY;
+        }
+        run0 = fmaxf(run0, fmaxf(Sv[j][0], Sv[j][2]));
+        run1 = fmaxf(run1, fmaxf(Sv[j][1], Sv[j][3]));
       }
       // ---- online softmax (per head: columns 2t and 2t+1 of this lane) ----
-      run0 = fmaxf(run0, fmaxf(Sv[0], Sv[2]));
-      run1 = fmaxf(run1, fmaxf(Sv[1], Sv[3]));
       if (__any_sync(FULL, run0 > m0 + kRefSlack || run1 > m1 + kRefSlack)) {
         // move the references to the current maxima of the columns (over the 8 row lanes)
         float n0 = run0, n1 = run1;
@@ -943,17 +935,22 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
           O[j][3] *= c1;
         }
       }
-      const float p0 = ex2(Sv[0] - m0), p1 = ex2(Sv[1] - m1);
-      const float p2 = ex2(Sv[2] - m0), p3 = ex2(Sv[3] - m1);
-      l0 += p0 + p2;
-      l1 += p1 + p3;
-      // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
-      const uint32_t pb0 = movmatrix_trans(pack_h2(p0, p1));
-      const uint32_t pb1 = movmatrix_trans(pack_h2(p2, p3));
+      uint32_t pb[NS][2];
+#pragma unroll
+      for (int j = 0; j < NS; ++j) {
+        const float p0 = ex2(Sv[j][0] - m0), p1 = ex2(Sv[j][1] - m1);
+        const float p2 = ex2(Sv[j][2] - m0), p3 = ex2(Sv[j][3] - m1);
+        l0 += p0 + p2;
+        l1 += p1 + p3;
+        // P^T fragments: (keys 2t,2t+1 | head g) and (keys 2t+8,2t+9 | head g)
+        pb[j][0] = movmatrix_trans(pack_h2(p0, p1));
+        pb[j][1] = movmatrix_trans(pack_h2(p2, p3));
+      }
       // ---- O^T += V^T P^T (256 dims x 8 heads) ----
-      {
+#pragma unroll
+      for (int j = 0; j < NS; ++j) {
         uint32_t rows[4];
-        const uint32_t r0 = sv + v_row_off;
+        const uint32_t r0 = my_ring + dd[j] * slot_sz + v_slot_off + v_row_off;
         rows[0] = r0;
         rows[1] = r0 + pitch_v;
         rows[2] = r0 + 8 * pitch_v;
@@ -962,25 +959,63 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
         if (!(p.debug & 8))
 #endif
         VL::run(rows, g, [&](int m, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-          mma16816(O[m], a0, a1, a2, a3, pb0, pb1);
+          mma16816(O[m], a0, a1, a2, a3, pb[j][0], pb[j][1]);
         });
       }
 #ifdef RD_TIMING_SWITCHES
       }
 #endif
-      // ---- hand the slot back; the last of the group's warps refills it ----
+      // ---- hand the slots back; the last of the group's warps refills each ----
       __syncwarp();
       uint32_t last = 0;
-      if (lane == 0) last = atom_add_acq_rel_shared(cnt0 + 4 * slot, 1u) == (uint32_t)(nkv - 1);
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < NS; ++j)
+          last |= (uint32_t)(atom_add_acq_rel_shared(cnt0 + 4 * pos[j], 1u) == (uint32_t)(nkv - 1)) << j;
+      }
       last = __shfl_sync(FULL, last, 0);
-      if (last) {
-        if (lane == 0) sts32(cnt0 + 4 * slot, 0u);
-        fill(gi, d);
+#pragma unroll
+      for (int j = 0; j < NS; ++j) {
+        if (last & (1u << j)) {
+          if (lane == 0) sts32(cnt0 + 4 * pos[j], 0u);
+          fill(gi, dd[j]);
+        }
       }
-      if (++d == D) {
-        d = 0;
-        ph ^= 1;
+    };
+    int d = 0;         // ring position of the next slot to consume
+    uint32_t ph = 0;   // and the parity its full barrier completes with
+    constexpr int kPerStep = G == 1 ? 2 : 1;   // two streams per warp where there are only four warps
+    for (int i = 0;; ++i) {
+      int pos[2], dd[2], cs[2];
+      int got = 0;
+      bool ok = true;
+      const int want = (kPerStep > 1 && D >= 3) ? kPerStep : 1;   // keep one slot of a short ring in flight
+      for (; got < want; ++got) {
+        pos[got] = gi * D + d;
+        dd[got] = d;
+        if (!mbar_wait(bar_full + 8 * pos[got], ph, p.status, 2)) {
+          ok = false;
+          break;
+        }
+        cs[got] = (int)lds32(sid0 + 4 * pos[got]);
+        if (cs[got] < 0) break;   // the group's slots have run out
+        if (++d == D) {
+          d = 0;
+          ph ^= 1;
+        }
       }
+      if (!ok) {
+        s_abort = 1;
+        break;
+      }
+#ifdef RD_TIMING_SWITCHES
+      if (i == 0) tr[3] = clock64();
+#endif
+      if (got == 2)
+        step(std::integral_constant<int, 2>(), pos, dd, cs);
+      else if (got == 1)
+        step(std::integral_constant<int, 1>(), pos, dd, cs);
+      if (got < want) break;
     }
     RD_TRACE(4);
     // row sums and true maxima: over the 8 key-row lanes of each head column

@@ -44,6 +44,14 @@
 #include "rd_common.cuh"
 #include "rd_internal.h"
 
+// Timing experiments (skip one pipeline stage, bit mask in PrefillArgs::debug) exist only
+// in builds with -DRD_TIMING_SWITCHES; a default build compiles them out.
+#ifdef RD_TIMING_SWITCHES
+#define RD_PF_DEBUG(p) ((p).debug)
+#else
+#define RD_PF_DEBUG(p) 0
+#endif
+
 namespace rd {
 
 constexpr int kPfM = 128;                 // query rows per CTA
@@ -334,7 +342,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
         if (*(volatile int *)&s_abort) break;
         const uint32_t full = bars + 8 * (kBarKFull + slot);
-        if (p.debug & 32) {
+        if (RD_PF_DEBUG(p) & 32) {
           mbar_arrive(full);
         } else {
           mbar_expect_tx(full, kPfKChunkBytes);
@@ -359,7 +367,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
         if (*(volatile int *)&s_abort) break;
         const uint32_t full = bars + 8 * (kBarVFull + slot);
-        if (p.debug & 32) {
+        if (RD_PF_DEBUG(p) & 32) {
           mbar_arrive(full);
           continue;
         }
@@ -400,7 +408,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           // K-major with 8-row groups 1 KB apart; four steps of 16 dims = 32 bytes each
           const uint64_t a0 = dq + (uint64_t)((c * (kPfM * 128)) >> 4);
           const uint64_t b0 = dk + (uint64_t)((slot * kPfKChunkBytes) >> 4);
-          if (!(p.debug & 8)) {
+          if (!(RD_PF_DEBUG(p) & 8)) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               tc_mma_f16(d_s, a0 + (uint64_t)(2 * kk), b0 + (uint64_t)(2 * kk), idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
@@ -438,7 +446,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           // groups 8 KB apart (LBO), 8-key groups 1 KB apart (SBO); 4 steps of 16 keys
           const uint64_t dvs = dv + (uint64_t)((slot * kPfVUnitBytes) >> 4);
           const uint32_t a_p = tmem + kTmemS + 128 * st + 32 * u;
-          if (!(p.debug & 4)) {
+          if (!(RD_PF_DEBUG(p) & 4)) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               tc_mma_f16_ts(tmem + kTmemO, a_p + 8 * kk, dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
@@ -518,8 +526,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       uint32_t pw[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = (p.debug & 1) ? __uint_as_float(s0[2 * i]) : ex2(__uint_as_float(s0[2 * i]) - m_ref);
-        const float p1 = (p.debug & 1) ? __uint_as_float(s0[2 * i + 1]) : ex2(__uint_as_float(s0[2 * i + 1]) - m_ref);
+        const float p0 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s0[2 * i]) : ex2(__uint_as_float(s0[2 * i]) - m_ref);
+        const float p1 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s0[2 * i + 1]) : ex2(__uint_as_float(s0[2 * i + 1]) - m_ref);
         ls[i & 3] += p0 + p1;
         pw[i] = pack_h2(p0, p1);
       }
@@ -527,8 +535,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       tmem_st16(pcol, pw);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = (p.debug & 1) ? __uint_as_float(s1[2 * i]) : ex2(__uint_as_float(s1[2 * i]) - m_ref);
-        const float p1 = (p.debug & 1) ? __uint_as_float(s1[2 * i + 1]) : ex2(__uint_as_float(s1[2 * i + 1]) - m_ref);
+        const float p0 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s1[2 * i]) : ex2(__uint_as_float(s1[2 * i]) - m_ref);
+        const float p1 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s1[2 * i + 1]) : ex2(__uint_as_float(s1[2 * i + 1]) - m_ref);
         ls[i & 3] += p0 + p1;
         pw[i] = pack_h2(p0, p1);
       }
@@ -655,10 +663,10 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   a.freq_base = freq_base;
   a.rope = make_rope_table(n_rot, freq_base);
   a.status = status;
-  {
-    const char *e = getenv("RD_PREFILL_DEBUG");
-    a.debug = e ? atoi(e) : 0;
-  }
+  a.debug = 0;
+#ifdef RD_TIMING_SWITCHES
+  if (const char *e = getenv("RD_PREFILL_DEBUG")) a.debug = atoi(e);
+#endif
   static bool attr_set[32] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return RD_ERR_CUDA;

@@ -44,15 +44,16 @@ static_assert(sizeof(XHeader) <= kShardHeaderBytes, "exchange header");
 __device__ __forceinline__ uint2 *xwords(unsigned char *xbuf) {
   return reinterpret_cast<uint2 *>(xbuf + kShardHeaderBytes);
 }
+// One (value, epoch) word = one aligned 8-byte scalar access: single-copy atomic by the
+// memory model, so a reader never pairs a fresh epoch with a stale value.
 __device__ __forceinline__ void st_word_sys(uint2 *p, float v, uint32_t epoch) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
-               "r"(epoch)
-               : "memory");
+  const unsigned long long w = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
