@@ -51,7 +51,8 @@ def mode_env_switches():
     pos = np.arange(nq, dtype=np.int32)
     wantp = oracle.attn(qf, kcf, vcf, pos, NKV, 1 / 16, 1, 1)
     outp = torch.full((nq, NH, HD), float("nan"), device="cuda")
-    rcp = lib.rd_fa2_prefill(rd.ptr(dev(qf)), rd.ptr(dev(kcf)), rd.ptr(dev(vcf)), rd.ptr(outp), rd.ptr(dev(pos)),
+    dqf, dkf, dvf, dpos = dev(qf), dev(kcf), dev(vcf), dev(pos)   # kept alive across the launch
+    rcp = lib.rd_fa2_prefill(rd.ptr(dqf), rd.ptr(dkf), rd.ptr(dvf), rd.ptr(outp), rd.ptr(dpos),
                              nq, nq - 1, nq, NH, NKV, HD, 1 / 16, rd.stream_ptr())
     torch.cuda.synchronize()
     errp = float(np.abs(outp.cpu().numpy() - wantp).max())
