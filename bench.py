@@ -207,6 +207,51 @@ def prefill_leg(rd, torch, peaks):
     for keys in (2048, 4096, 8192):
         res[f"fa2_window_512q_{keys}keys"] = run(512, keys - 512, False)
     res["causal_8192x8192"] = run(8192, 0, False)
+
+    # quantized caches: the typed entry (caches expanded once to f16, then the tensor-core
+    # kernel) against the per-token path the reference's chunk dispatcher would take
+    # (rd_attn_batch == attn_batch_launch: every token re-streams its prefix)
+    def run_q4(n_q, keys):
+        kc = torch.empty(keys * NKV * 144, dtype=torch.uint8, device="cuda")
+        vc = torch.empty_like(kc)
+        st = rd.stream_ptr()
+        rd.check(L.rd_kv_fill(3, rd.ptr(kc), keys * NKV, HD, 11, st))
+        rd.check(L.rd_kv_fill(3, rd.ptr(vc), keys * NKV, HD, 22, st))
+        q = torch.randn(n_q, NH, HD, device="cuda")
+        o = torch.empty_like(q)
+        pos = torch.arange(keys - n_q, keys, dtype=torch.int32, device="cuda")
+        nb = L.rd_attn_prefill_workspace_bytes(3, 3, keys, NKV, HD)
+        ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+
+        def typed():
+            rd.check(L.rd_attn_prefill_typed(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), None, rd.ptr(pos), n_q,
+                                             keys, NH, NKV, HD, SCALE, 3, 3, 0, 0.0, rd.ptr(ws), nb, rd.stream_ptr()))
+
+        def per_token():
+            rd.check(L.rd_attn_batch(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(pos), n_q, NH, NKV, HD,
+                                     SCALE, 3, 3, rd.stream_ptr()))
+        out = {}
+        for name, fn, reps in (("typed_tensor_core", typed, 20), ("per_token_path", per_token, 3)):
+            fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()      # replayed, like the other rows: no host launch cost
+            with torch.cuda.graph(g):
+                fn()
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            out[name + "_us"] = e0.elapsed_time(e1) / reps * 1e3
+        flops = 4 * HD * NH * sum(keys - n_q + t + 1 for t in range(n_q))
+        out["tflops"] = flops / out["typed_tensor_core_us"] / 1e6
+        out["frac"] = out["tflops"] / peak
+        out["speedup_over_per_token_path"] = out["per_token_path_us"] / out["typed_tensor_core_us"]
+        return out
+    res["q4_0_cache_512q_8192keys"] = run_q4(512, 8192)
     return res
 
 

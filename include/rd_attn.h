@@ -334,6 +334,21 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
                           int head_dim, float scale, int n_rot, float freq_base, void *stream);
 
+/* ---- causal prefill over caches of ANY type pair on the tensor cores: what the reference
+ * serves with its chunk path, attn_split_batch_launch (include/rdna4/attn.cuh:958-1049, all
+ * 6 x 6 K x V types; dispatch src/graph.cuh:1486-1527), where every one of the n_q tokens
+ * re-streams and re-expands its prefix. Here the caches that are not f16 are expanded ONCE
+ * into `workspace` (rd_attn_prefill_workspace_bytes; 0 for f16/f16) with the exact values
+ * of the reference's dequantizing loads (kv.h:174-368) rounded to f16, and the tcgen05
+ * prefill kernel runs over that copy. Arguments as rd_attn_prefill_fused; token i attends
+ * keys 0..pos[i], keys_total rows must exist. No allocation, no host synchronisation. */
+size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int keys_total, int n_head_kv,
+                                       int head_dim);
+int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o, const float *gate,
+                          const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
+                          int head_dim, float scale, int k_type, int v_type, int n_rot, float freq_base,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- device status: 0, or RD_ERR_DEVICE if any kernel launched through this
  * library on the current device gave up on a bounded wait since the last call.
  * Synchronises the device; meant for tests and debugging, not for the hot path. */

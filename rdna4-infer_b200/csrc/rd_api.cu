@@ -793,6 +793,47 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
                         n_rot, freq_base, stream);
 }
 
+size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int keys_total, int n_head_kv, int head_dim) {
+  if (!known_type(k_type) || !known_type(v_type) || keys_total <= 0 || n_head_kv < 1 || head_dim != kHeadDim)
+    return 0;
+  const size_t one = align256((size_t)keys_total * n_head_kv * kHeadDim * 2);
+  return (k_type != RD_KV_F16 ? one : 0) + (v_type != RD_KV_F16 ? one : 0);
+}
+
+int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o, const float *gate,
+                          const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
+                          int head_dim, float scale, int k_type, int v_type, int n_rot, float freq_base,
+                          void *workspace, size_t workspace_bytes, void *stream) {
+  int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  if (rc != RD_OK) return rc;
+  if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
+  if (k == nullptr || v == nullptr) return RD_ERR_NULL;
+  if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
+  const size_t need = rd_attn_prefill_workspace_bytes(k_type, v_type, keys_total, n_head_kv, head_dim);
+  if (need > 0) {
+    if (workspace == nullptr || workspace_bytes < need) return RD_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
+  }
+  // caches that are not f16 are expanded once into the workspace -- one pass shared by
+  // every query tile and every head, where the per-token path re-reads and re-expands
+  // the prefix for each of the n_q tokens
+  const int64_t n_values = (int64_t)keys_total * n_head_kv * kHeadDim;
+  unsigned char *w = (unsigned char *)workspace;
+  const void *k16 = k, *v16 = v;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (k_type != RD_KV_F16) {
+    if ((rc = launch_kv_dequant_f16(k_type, k, w, n_values, st)) != RD_OK) return rc;
+    k16 = w;
+    w += align256((size_t)n_values * 2);
+  }
+  if (v_type != RD_KV_F16) {
+    if ((rc = launch_kv_dequant_f16(v_type, v, w, n_values, st)) != RD_OK) return rc;
+    v16 = w;
+  }
+  return prefill_common(q, k16, v16, o, gate, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
+                        n_rot, freq_base, stream);
+}
+
 int rd_device_status(void) {
   int dev;
   int rc = current_device(&dev);

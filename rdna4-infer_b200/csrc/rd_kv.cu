@@ -233,4 +233,89 @@ int launch_sigmoid_gate(float *g, float *y, int64_t n, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
 }
 
+// ---- stored rows -> f16 rows (the dequantizing loads of include/rdna4/kv.h:174-368) ------
+// One thread per 8 consecutive elements (one 16-byte store); the value is formed in f32
+// exactly as kv_load does (d * q, d * (n - 8), d * (n5 - 16), d * n + m) and rounded once to
+// f16 -- the same value the decode kernel's fragment loaders hand to the tensor cores. Feeds
+// the tensor-core prefill kernel when the caches are not f16.
+__device__ __forceinline__ uint32_t ld16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+
+// elements [8 * oct, 8 * oct + 8) of the 32-value block at b
+template <int T>
+__device__ __forceinline__ void dequant8(const uint8_t *b, int oct, float (&x)[8]) {
+  if (T == RD_KV_Q8_0) {
+    const float d = f16_bits_to_f32((uint16_t)ld16(b));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = ld16(b + 2 + 8 * oct + 2 * i);
+      x[2 * i] = d * (float)(int8_t)(w & 0xff);
+      x[2 * i + 1] = d * (float)(int8_t)(w >> 8);
+    }
+    return;
+  }
+  // 4-bit layouts: element j < 16 is the low nibble of byte j, element j + 16 the high one
+  constexpr int QS = T == RD_KV_Q4_0 ? 2 : T == RD_KV_Q4_1 ? 4 : 6;
+  const float d = f16_bits_to_f32((uint16_t)ld16(b));
+  const float m = T == RD_KV_Q4_1 ? f16_bits_to_f32((uint16_t)ld16(b + 2)) : 0.f;
+  const uint32_t qh = T == RD_KV_Q5_0 ? (ld16(b + 2) | (ld16(b + 4) << 16)) : 0u;
+  const int sh = oct >= 2 ? 4 : 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w = ld16(b + QS + 8 * (oct & 1) + 2 * i);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int n = (int)((w >> (8 * h + sh)) & 15u);
+      const int j = 8 * oct + 2 * i + h;
+      if (T == RD_KV_Q4_0) x[2 * i + h] = d * (float)(n - 8);
+      if (T == RD_KV_Q4_1) x[2 * i + h] = __fadd_rn(__fmul_rn(d, (float)n), m);
+      if (T == RD_KV_Q5_0) {
+        n |= (int)((qh >> j) & 1u) << 4;
+        x[2 * i + h] = d * (float)(n - 16);
+      }
+    }
+  }
+}
+
+template <int T>
+__global__ void __launch_bounds__(256)
+kv_dequant_f16_kernel(const uint8_t *__restrict__ src, uint4 *__restrict__ dst, int64_t n_octs) {
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_octs; o += (int64_t)gridDim.x * blockDim.x) {
+    float x[8];
+    if (T == RD_KV_F32) {
+      const float4 a = reinterpret_cast<const float4 *>(src)[2 * o], c = reinterpret_cast<const float4 *>(src)[2 * o + 1];
+      x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = c.x, x[5] = c.y, x[6] = c.z, x[7] = c.w;
+    } else if (T == RD_KV_F16) {
+      dst[o] = reinterpret_cast<const uint4 *>(src)[o];
+      continue;
+    } else {
+      constexpr int BB = row_bytes(T) / 8;
+      dequant8<T>(src + (o >> 2) * BB, (int)(o & 3), x);
+    }
+    dst[o] = make_uint4(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]), pack_h2(x[4], x[5]), pack_h2(x[6], x[7]));
+  }
+}
+
+template <int T>
+static void dequant_launch(const void *src, void *dst, int64_t n_octs, cudaStream_t st) {
+  const int64_t want = (n_octs + 255) / 256;
+  const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  kv_dequant_f16_kernel<T><<<grid, 256, 0, st>>>((const uint8_t *)src, (uint4 *)dst, n_octs);
+}
+
+int launch_kv_dequant_f16(int type, const void *src, void *dst, int64_t n_values, cudaStream_t st) {
+  if (n_values % 32 != 0) return RD_ERR_SHAPE;
+  const int64_t n_octs = n_values / 8;
+  if (n_octs == 0) return RD_OK;
+  switch (type) {
+    case RD_KV_F32: dequant_launch<RD_KV_F32>(src, dst, n_octs, st); break;
+    case RD_KV_F16: dequant_launch<RD_KV_F16>(src, dst, n_octs, st); break;
+    case RD_KV_Q8_0: dequant_launch<RD_KV_Q8_0>(src, dst, n_octs, st); break;
+    case RD_KV_Q4_0: dequant_launch<RD_KV_Q4_0>(src, dst, n_octs, st); break;
+    case RD_KV_Q5_0: dequant_launch<RD_KV_Q5_0>(src, dst, n_octs, st); break;
+    case RD_KV_Q4_1: dequant_launch<RD_KV_Q4_1>(src, dst, n_octs, st); break;
+    default: return RD_ERR_TYPE;
+  }
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+}
+
 }  // namespace rd

@@ -98,3 +98,40 @@ def test_prefill_fused_rope_and_gate(G, oracle, rd):
     assert (G.host(vc) == vc_o).all()
     got = run_prefill(G, rd, q, G.host(kc), G.host(vc), pos, n_q, nkv, gate=gate, n_rot=64)
     check_attn(got, want, what="fused rope + gate prefill-512")
+
+
+@pytest.mark.parametrize("kt,vt", [(3, 3), (2, 2), (4, 5), (2, 1)])
+@pytest.mark.parametrize("pos0", [0, 1536, 7680])
+def test_typed_prefill_over_quantized_caches(G, oracle, rd, kt, vt, pos0):
+    """512 new tokens over (q4_0,q4_0), (q8_0,q8_0), (q5_0,q4_1), (q8_0,f16) caches through
+    rd_attn_prefill_typed (caches expanded once to f16, then the tensor-core kernel) against
+    the oracle's attention over the same stored bytes; t = pos[qt] as in
+    attn_split_batch_launch (include/rdna4/attn.cuh:958-1049)."""
+    import torch
+    n_q = 512
+    keys_total = pos0 + n_q
+    nh, nkv = (24, 4) if keys_total <= 1024 else (6, 1)   # keep the CPU oracle quick
+    rng = np.random.default_rng(100 * kt + 10 * vt + pos0)
+    K = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    V = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    q = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    gate = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(kt, K), oracle.kv_store_rows(vt, V)
+    pos = np.arange(pos0, keys_total, dtype=np.int32)
+    y = oracle.attn(q, kc, vc, pos, nkv, 1 / 16, kt, vt)
+    _, want = oracle.sigmoid_gate(gate.copy(), y)
+    nbytes = rd.lib.rd_attn_prefill_workspace_bytes(kt, vt, keys_total, nkv, 256)
+    assert nbytes == sum(((keys_total * nkv * 512 + 255) // 256) * 256 for t in (kt, vt) if t != 1)
+    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device="cuda")
+    dq, dk, dv, dg, dpos = G.dev(q), G.dev(kc), G.dev(vc), G.dev(gate), G.dev(pos)
+    out = G.poison(q.shape)
+    rd.check(rd.lib.rd_attn_prefill_typed(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), rd.ptr(dg), rd.ptr(dpos),
+                                          n_q, keys_total, nh, nkv, 256, 1 / 16, kt, vt, 0, 0.0, rd.ptr(ws), nbytes,
+                                          G.st()))
+    torch.cuda.synchronize()
+    assert rd.lib.rd_device_status() == rd.OK
+    check_attn(G.host(out), want, what=f"typed prefill {kt}/{vt} pos0={pos0}")
+    if nbytes:   # a workspace that is too small is refused before anything runs
+        assert rd.lib.rd_attn_prefill_typed(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), None, rd.ptr(dpos), n_q,
+                                            keys_total, nh, nkv, 256, 1 / 16, kt, vt, 0, 0.0, rd.ptr(ws), nbytes - 256,
+                                            G.st()) == rd.ERR_WORKSPACE
