@@ -720,9 +720,10 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
   a.scale = scale;
   a.n_splits = S;
   a.status = status;
-  cudaStream_t st = (cudaStream_t)stream;
-  if ((rc = launch_decode(k_type, v_type, a, st)) != RD_OK) return rc;
-  return launch_shard_exchange((const float *)workspace, S, out, gate, n_head, g, status, st);
+  a.push = &g;   // the decode launch runs the whole exchange in its epilogue
+  a.push_out = out;
+  a.push_gate = gate;
+  return launch_decode(k_type, v_type, a, (cudaStream_t)stream);
 }
 
 int rd_attn_merge(const float *partial, float *out, int n_rows, int head_dim, int n_splits,

@@ -43,6 +43,7 @@
 
 #include "rd_internal.h"
 #include "rd_quant.cuh"
+#include "rd_shard.cuh"
 
 namespace rd {
 
@@ -583,6 +584,13 @@ struct DecodeKernelArgs {
   const float *k_new;
   const float *v_new;
   int new_row;
+  // Context-sharded calls (single-sequence launches, push.world > 0): once every CTA's
+  // records are written, the first n_head * 4 CTAs reduce them per (head, dim quarter),
+  // store the parts into every rank's exchange buffer, wait for the other ranks' parts and
+  // merge -- the whole exchange of rd_shard.cu inside this launch.
+  ShardPeers push;
+  float *x_out;    // [n_head][256]: the merged output of a context-sharded call
+  float *x_gate;   // optional fused sigmoid gate of that output
 };
 
 // acq_rel: the slot reads of the arriving warp happen before the refill the last
@@ -1107,6 +1115,65 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
       }
     }
   }
+  if constexpr (!MULTI) {
+    if (p.push.world > 0) {
+      // Context-sharded call: the exchange of rd_shard.cu inside this launch. Every CTA
+      // reports its records written; the first n_head * 4 CTAs then take one (head, dim
+      // quarter) each: wait (bounded) for all CTAs, reduce the launch's records to one part,
+      // store it into every rank's buffer, wait (bounded) for the other ranks' parts and
+      // merge them into the output quarter.
+      constexpr int NGW = NT / 16;
+      float *s_pacc = reinterpret_cast<float *>(smem + kRingOffset);   // over the ring: the planes
+      float *s_pl = s_pacc + NGW * kPushDims;                          // have been read by the time
+      float *s_pgm = s_pl + NGW;                                       // the barrier below is passed
+      int &s_go = s_abort;   // free again: the abort state was read into `aborted` above
+      XHeader *me = reinterpret_cast<XHeader *>(p.push.x[p.push.rank]);
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&me->epoch) + 1;
+      uint32_t *arrived = &me->push_count[epoch & 1];
+      __syncthreads();   // this CTA's record stores are issued
+      if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(arrived, 1u);
+      }
+      const int n_roles = p.n_head * kQuarters;
+      if ((int)blockIdx.x < n_roles) {
+        if (threadIdx.x == 0) {
+          int ok = 1;
+          if (*reinterpret_cast<volatile uint32_t *>(arrived) < gridDim.x) {
+            const unsigned long long t0 = global_ns();
+            unsigned polls = 0;
+            while (*reinterpret_cast<volatile uint32_t *>(arrived) < gridDim.x) {
+              if ((++polls & 63u) == 0 && global_ns() - t0 > p.push.wait_ns) {
+                ok = 0;
+                break;
+              }
+            }
+          }
+          if (!ok && p.status != nullptr && atomicExch(&p.status->timeout_flag, 1) == 0) p.status->where = 90;
+          __threadfence();
+          s_go = ok;
+        }
+        __syncthreads();
+        for (int role = blockIdx.x; role < n_roles; role += gridDim.x) {
+          const int row = role / kQuarters, quarter = role % kQuarters;
+          if (s_go)
+            shard_push_part_wide<NT>(p.partial, (int)gridDim.x, p.n_head, row, quarter, p.push, epoch, s_pacc, s_pl,
+                                     s_pgm, 8);
+          if (threadIdx.x < kPushDims)
+            shard_merge_part(p.x_out, p.x_gate, p.n_head, row, quarter, threadIdx.x, p.push, epoch, p.status);
+          if (threadIdx.x == 0) {
+            const uint32_t prev = atomicAdd(&me->merge_count, 1u);
+            if (prev == (uint32_t)n_roles - 1) {
+              me->merge_count = 0;
+              me->push_count[epoch & 1] = 0;
+              __threadfence();
+              me->epoch = epoch;  // every CTA of the launch read the old value before it arrived
+            }
+          }
+        }
+      }
+    }
+  }
 #ifdef RD_TIMING_SWITCHES
   if (p.debug & 32) {
     __syncthreads();
@@ -1196,6 +1263,11 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
   k.k_new = a.k_new;
   k.v_new = a.v_new;
   k.new_row = a.new_row;
+  if (a.push != nullptr && a.n_tok == 1) {   // memset above: world 0 = no exchange
+    k.push = *a.push;
+    k.x_out = a.push_out;
+    k.x_gate = a.push_gate;
+  }
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
   return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3(4 * G * 32), smem, st, k) == cudaSuccess
              ? RD_OK

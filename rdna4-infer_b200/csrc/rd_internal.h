@@ -33,6 +33,21 @@ int launch_pre_attn(int kt, int vt, const float *qg, const float *k_src, const f
                     void *k_rows, void *v_rows, const int32_t *pos, int n_tok, int n_head, int nkv,
                     int n_rot, float freq_base, cudaStream_t st);
 
+// ---- rd_shard.cu (types)
+// Exchange buffers of a context-sharded group, as mapped into this process: x[r] is
+// rank r's buffer (x[rank] the local one): kShardHeaderBytes of header, then
+// [2 parities][world][n_head][4 dim quarters][kXPart] record parts of 8-byte words
+// (f32 value, epoch).
+constexpr int kShardMaxWorld = 8;
+constexpr int kShardMaxHeads = 32;
+constexpr int kXPart = 2 + 64;  // (m, l) + one quarter of the accumulator
+constexpr size_t kShardHeaderBytes = 256;
+struct ShardPeers {
+  unsigned char *x[kShardMaxWorld];
+  int rank;
+  int world;
+  unsigned long long wait_ns;  // how long the merge waits for the other ranks' records
+};
 // ---- rd_decode_*.cu
 // One launch of the split-KV decode kernel: grid (n_splits, n_tok). Token i attends
 // keys key_begin..(pos ? pos[i] : t). Writes n_splits records per (token, head) into
@@ -57,6 +72,12 @@ struct DecodeArgs {
   const float *k_new = nullptr;
   const float *v_new = nullptr;
   int new_row = 0;
+  // Context-sharded call (single token): the launch also runs the exchange -- reduces its
+  // records per (head, dim quarter), stores the parts into every rank's buffer, waits for
+  // the other ranks' parts and writes the merged (optionally gated) output to push_out.
+  const ShardPeers *push = nullptr;
+  float *push_out = nullptr;    // [n_head][256]
+  float *push_gate = nullptr;   // optional
 };
 int launch_decode(int kt, int vt, const DecodeArgs &a, cudaStream_t st);
 
@@ -148,21 +169,7 @@ int launch_merge_records(const float *partial, float *records, int n_rows, int n
 int launch_merge_multi(const DecodeSeq *dev_seqs, const float *records, int n_seq, int q_len,
                        int n_head, cudaStream_t st);
 
-// ---- rd_shard.cu
-// Exchange buffers of a context-sharded group, as mapped into this process: x[r] is
-// rank r's buffer (x[rank] the local one): kShardHeaderBytes of header, then
-// [2 parities][world][n_head][4 dim quarters][kXPart] record parts of 8-byte words
-// (f32 value, epoch).
-constexpr int kShardMaxWorld = 8;
-constexpr int kShardMaxHeads = 32;
-constexpr int kXPart = 2 + 64;  // (m, l) + one quarter of the accumulator
-constexpr size_t kShardHeaderBytes = 256;
-struct ShardPeers {
-  unsigned char *x[kShardMaxWorld];
-  int rank;
-  int world;
-  unsigned long long wait_ns;  // how long the merge waits for the other ranks' records
-};
+// ---- rd_shard.cu (launchers)
 // partial [n_head][n_in][258] (this rank's split records) -> one record per head stored
 // into every rank's buffer, then this call's epoch into every rank's flag.
 int launch_shard_push(const float *partial, int n_in, int n_head, const ShardPeers &g,

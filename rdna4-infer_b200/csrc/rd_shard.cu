@@ -28,54 +28,11 @@
 // MERGE only) for callers that compute the records themselves.
 #include "rd_common.cuh"
 #include "rd_internal.h"
+#include "rd_shard.cuh"
 
 namespace rd {
 
-constexpr int kPushDims = 64;
 constexpr int kPushGroups = 16;
-constexpr int kQuarters = kHeadDim / kPushDims;
-
-struct XHeader {
-  uint32_t epoch;        // calls completed on this rank
-  uint32_t merge_count;  // CTAs of the running merge that are done
-};
-static_assert(sizeof(XHeader) <= kShardHeaderBytes, "exchange header");
-
-__device__ __forceinline__ uint2 *xwords(unsigned char *xbuf) {
-  return reinterpret_cast<uint2 *>(xbuf + kShardHeaderBytes);
-}
-// One (value, epoch) word = one aligned 8-byte scalar access: single-copy atomic by the
-// memory model, so a reader never pairs a fresh epoch with a stale value.
-__device__ __forceinline__ void st_word_sys(uint2 *p, float v, uint32_t epoch) {
-  const unsigned long long w = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
-  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
-}
-__device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
-  unsigned long long w;
-  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-  return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Spins until the word carries `epoch`; false when wait_ns ran out first. The clock is
-// only consulted every 64 polls: reading it costs as much as a poll.
-__device__ __forceinline__ bool wait_word(const uint2 *p, uint32_t epoch, unsigned long long wait_ns,
-                                          float &value) {
-  uint2 w = ld_word_sys(p);
-  if (w.y != epoch) {
-    const unsigned long long t0 = global_ns();
-    unsigned polls = 0;
-    do {
-      if ((++polls & 63u) == 0 && global_ns() - t0 > wait_ns) return false;
-      w = ld_word_sys(p);
-    } while (w.y != epoch);
-  }
-  value = __uint_as_float(w.x);
-  return true;
-}
 
 // grid (n_head, 4 dim quarters), 1024 threads = 16 record groups x 64 dims. CTA (head,
 // quarter) handles that quarter of the head's record in both halves:
@@ -95,127 +52,20 @@ shard_exchange_kernel(const float *__restrict__ partial, int n_in, float *__rest
 
   const int row = blockIdx.x, quarter = blockIdx.y;
   const int tx = threadIdx.x % kPushDims, ty = threadIdx.x / kPushDims;
-  const int d = quarter * kPushDims + tx;
   XHeader *me = reinterpret_cast<XHeader *>(g.x[g.rank]);
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&me->epoch) + 1;
   const int par = epoch & 1;
-  // word index of part (parity, source rank r, head row, quarter): + r * rstride
-  const size_t rstride = (size_t)n_head * kQuarters * kXPart;
-  const size_t part0 = (size_t)par * g.world * rstride + ((size_t)row * kQuarters + quarter) * kXPart;
-
-  if (PUSH) {
-    // one pass, as in merge_kernel: group ty walks records ty, ty+16, ... with four loads
-    // in flight and a local log-sum-exp; the 16 groups meet in shared memory
-    const float *base = partial + (size_t)row * n_in * kRec;
-    float mloc = -INFINITY, acc = 0.f, ll = 0.f;
-    for (int s0 = ty; s0 < n_in; s0 += 4 * kPushGroups) {
-      float m4[4], a4[4], l4[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int sidx = s0 + k * kPushGroups;
-        m4[k] = -INFINITY;
-        a4[k] = l4[k] = 0.f;
-        if (sidx < n_in) {
-          const float *rec = base + (size_t)sidx * kRec;
-          m4[k] = rec[0];
-          a4[k] = rec[2 + d];
-          if (tx == 0) l4[k] = rec[1];
-        }
-      }
-      const float mb = fmaxf(fmaxf(mloc, fmaxf(m4[0], m4[1])), fmaxf(m4[2], m4[3]));
-      if (mb != -INFINITY) {
-        const float f = expf(mloc - mb);
-        acc *= f;
-        ll *= f;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (m4[k] != -INFINITY) {
-            const float w = expf(m4[k] - mb);
-            acc = fmaf(a4[k], w, acc);
-            ll = fmaf(l4[k], w, ll);
-          }
-        }
-        mloc = mb;
-      }
-    }
-    s_acc[ty][tx] = acc;
-    if (tx == 0) {
-      s_l[ty] = ll;
-      s_gm[ty] = mloc;
-    }
-    __syncthreads();
-    if (ty == 0) {
-      float mm = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < kPushGroups; ++i) mm = fmaxf(mm, s_gm[i]);
-      float a = 0.f, l = 0.f;
-#pragma unroll
-      for (int i = 0; i < kPushGroups; ++i) {
-        if (s_gm[i] != -INFINITY) {
-          const float w = expf(s_gm[i] - mm);
-          a = fmaf(s_acc[i][tx], w, a);
-          l = fmaf(s_l[i], w, l);
-        }
-      }
-      // every quarter carries its own copy of (m, l): part layout [m, l, 64 values]
-      const size_t mine = part0 + (size_t)g.rank * rstride;
-      for (int r = 0; r < g.world; ++r) {
-        uint2 *rec = xwords(g.x[r]) + mine;
-        st_word_sys(rec + 2 + tx, a, epoch);
-        if (tx == 0) {
-          st_word_sys(rec, mm, epoch);
-          st_word_sys(rec + 1, l, epoch);
-        }
-      }
-    }
-  }
+  if (PUSH)
+    shard_push_part<kPushGroups>(partial, n_in, n_head, row, quarter, tx, ty, g, epoch, s_acc, s_l, s_gm, 1);
 
   if (MERGE) {
-    if (ty == 0) {
-      const uint2 *recs = xwords(g.x[g.rank]) + part0;
-      bool ok = true;
-      float m_r[kShardMaxWorld], l_r[kShardMaxWorld], a_r[kShardMaxWorld];
-#pragma unroll
-      for (int r = 0; r < kShardMaxWorld; ++r) {
-        m_r[r] = -INFINITY;
-        l_r[r] = a_r[r] = 0.f;
-        if (r < g.world && ok) {
-          const uint2 *rec = recs + r * rstride;
-          ok = wait_word(rec, epoch, g.wait_ns, m_r[r]) && wait_word(rec + 1, epoch, g.wait_ns, l_r[r]) &&
-               wait_word(rec + 2 + tx, epoch, g.wait_ns, a_r[r]);
-        }
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok && tx == 0 && status != nullptr && atomicExch(&status->timeout_flag, 1) == 0)
-        status->where = 100 + g.rank;   // some rank never pushed: zeros, reported
-      float mm = -INFINITY;
-#pragma unroll
-      for (int r = 0; r < kShardMaxWorld; ++r) mm = fmaxf(mm, m_r[r]);
-      float a = 0.f, l = 0.f;
-      if (mm != -INFINITY) {
-#pragma unroll
-        for (int r = 0; r < kShardMaxWorld; ++r) {
-          const float w = expf(m_r[r] - mm);   // 0 for an empty part (m = -inf)
-          if (w > 0.f) {
-            a = fmaf(a_r[r], w, a);
-            l = fmaf(l_r[r], w, l);
-          }
-        }
-      }
-      float o = (ok && mm != -INFINITY && l > 0.f) ? a / l : 0.f;
-      if (gate != nullptr) {
-        float *gp = gate + (size_t)row * kHeadDim + d;
-        const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
-        *gp = sg;
-        o *= sg;
-      }
-      out[(size_t)row * kHeadDim + d] = o;
-    }
+    if (ty == 0) shard_merge_part(out, gate, n_head, row, quarter, tx, g, epoch, status);
     __syncthreads();
     if (threadIdx.x == 0) {
       const uint32_t prev = atomicAdd(&me->merge_count, 1u);
       if (prev == gridDim.x * gridDim.y - 1) {
         me->merge_count = 0;
+        me->push_count[par] = 0;  // arrival counter of a fused decode + push launch of this call
         me->epoch = epoch;  // every CTA read the old value before it arrived here
       }
     }
