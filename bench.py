@@ -439,6 +439,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--fused-append", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"], help=argparse.SUPPRESS)
+    # profiling aid: W warm-up steps only (no 300 ms floor) and no extra rounds, so that a
+    # capture under ncu sees few launches before the one it wants
+    ap.add_argument("--short", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -632,7 +635,7 @@ def main():
     # each graph, interleaved, give the mean and the best round.
     def warm(gph, host_io):
         done = timed(gph, W, host_io)
-        while done < 300.0:
+        while done < 300.0 and not args.short:
             done += timed(gph, max(W, 50), host_io)
     warm(g_dev, False)
     sampler.start()
@@ -640,7 +643,7 @@ def main():
     n_launch = per_step * K
     warm(g_e2e, True)
     ms_e2e = timed(g_e2e, K, True)
-    ROUNDS = 10
+    ROUNDS = 0 if args.short else 10
     r_dev, r_e2e = [], []
     for _ in range(ROUNDS):
         r_dev.append(timed(g_dev, K, False))
@@ -766,12 +769,13 @@ def main():
                 "h2d_bytes_per_step": in_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4},
         "gpu_launches": n_launch, "cuda_graph": g_dev is not None, "roofline": roofline, "clocks": clocks,
         "us_per_layer": ms_dev / K / n_layers * 1e3,
-        "rounds": {"n": ROUNDS, "steps_each": K, "warmup_ms_min": 300,
-                   "value_mean": bytes_step * K * ROUNDS / (sum(r_dev) * 1e-3) / 1e9,
-                   "value_best": bytes_step * K / (min(r_dev) * 1e-3) / 1e9,
-                   "e2e_mean": bytes_step * K * ROUNDS / (sum(r_e2e) * 1e-3) / 1e9,
-                   "e2e_best": bytes_step * K / (min(r_e2e) * 1e-3) / 1e9},
     }
+    if ROUNDS:
+        out["rounds"] = {"n": ROUNDS, "steps_each": K, "warmup_ms_min": 300,
+                         "value_mean": bytes_step * K * ROUNDS / (sum(r_dev) * 1e-3) / 1e9,
+                         "value_best": bytes_step * K / (min(r_dev) * 1e-3) / 1e9,
+                         "e2e_mean": bytes_step * K * ROUNDS / (sum(r_e2e) * 1e-3) / 1e9,
+                         "e2e_best": bytes_step * K / (min(r_e2e) * 1e-3) / 1e9}
     out["config"]["exchange"] = exchange
     if rank == 0 and world == 1 and args.leg == "all":
         out["prefill"] = prefill_leg(rd, torch, peaks)
