@@ -220,7 +220,7 @@ def prefill_leg(rd, torch, peaks):
         q = torch.randn(n_q, NH, HD, device="cuda")
         o = torch.empty_like(q)
         pos = torch.arange(keys - n_q, keys, dtype=torch.int32, device="cuda")
-        nb = L.rd_attn_prefill_workspace_bytes(3, 3, keys, NKV, HD)
+        nb = L.rd_attn_prefill_workspace_bytes(3, 3, n_q, keys, NH, NKV, HD)
         ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
 
         def typed():

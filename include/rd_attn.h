@@ -244,9 +244,11 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
  *                    When it runs out the kernel stores zeros, records the event
  *                    (rd_device_status returns RD_ERR_DEVICE) and returns normally.
  *   workspace        rd_attn_workspace_bytes(1, ...), 256-byte aligned.
- * The call is two launches on `stream` and nothing else (no copy, no allocation
- * after the first call on a device), and keeps its call counter in the exchange
- * buffer, so it can be captured into a CUDA graph and replayed. world <= 8.
+ * The call is ONE launch on `stream` and nothing else (no copy, no allocation): the
+ * decode kernel's first n_head * 4 CTAs wait for the launch's records, reduce them, store
+ * the parts into every rank's buffer, wait (bounded) for the other ranks' parts and merge.
+ * The call counter lives in the exchange buffer, so the call can be captured into a CUDA
+ * graph and replayed. world <= 8.
  *
  * rd_attn_shard_push / rd_attn_shard_merge are the two halves of the exchange for a
  * caller that computes the split records itself (rd_attn_decode_split with out == NULL,
@@ -316,7 +318,12 @@ int rd_attn_split_batch(const float *q, const void *k, const void *v, float *out
  * include/rdna4/attn_fa2.cuh:174-207. f16/f16 caches; runs on tcgen05 tensor cores with
  * TMEM accumulators. The admission window is wider than the reference's (any n_q >= 1
  * and any key count), since the tensor-core kernel has no measured-only range to
- * protect. keys_total rows must exist in the caches; token i attends keys 0..pos[i]. */
+ * protect. keys_total rows must exist in the caches; token i attends keys 0..pos[i].
+ * When n_q * n_head / 128 CTAs would leave most SMs idle, the keys are split over more CTAs
+ * and a second launch merges per-split records; rd_fa2_prefill and rd_attn_prefill_fused
+ * keep those records in the library's own per-device workspace (grown on demand like that
+ * of the allocating launchers above: warm up once before a stream capture), while
+ * rd_attn_prefill_typed keeps them in the caller's workspace and never allocates. */
 int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head, int n_head_kv,
                           int head_dim);
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
@@ -338,12 +345,12 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
  * serves with its chunk path, attn_split_batch_launch (include/rdna4/attn.cuh:958-1049, all
  * 6 x 6 K x V types; dispatch src/graph.cuh:1486-1527), where every one of the n_q tokens
  * re-streams and re-expands its prefix. Here the caches that are not f16 are expanded ONCE
- * into `workspace` (rd_attn_prefill_workspace_bytes; 0 for f16/f16) with the exact values
- * of the reference's dequantizing loads (kv.h:174-368) rounded to f16, and the tcgen05
- * prefill kernel runs over that copy. Arguments as rd_attn_prefill_fused; token i attends
+ * into `workspace` (rd_attn_prefill_workspace_bytes, which also covers the records of the
+ * key split below) with the exact values of the reference's dequantizing loads
+ * (kv.h:174-368) rounded to f16, and the tcgen05 prefill kernel runs over that copy. Arguments as rd_attn_prefill_fused; token i attends
  * keys 0..pos[i], keys_total rows must exist. No allocation, no host synchronisation. */
-size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int keys_total, int n_head_kv,
-                                       int head_dim);
+size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int n_q, int keys_total, int n_head,
+                                       int n_head_kv, int head_dim);
 int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o, const float *gate,
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
                           int head_dim, float scale, int k_type, int v_type, int n_rot, float freq_base,

@@ -761,9 +761,12 @@ int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head,
   return check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type) == RD_OK ? 1 : 0;
 }
 
+// records / record_bytes: caller memory for the key-split records, or NULL: the library's
+// own grown workspace is used then (see the note on allocating launchers in rd_attn.h).
 static int prefill_common(const float *q, const void *k, const void *v, float *o, const float *gate,
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
-                          int head_dim, float scale, int n_rot, float freq_base, void *stream) {
+                          int head_dim, float scale, int n_rot, float freq_base, void *stream,
+                          void *records = nullptr, size_t record_bytes = 0) {
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, RD_KV_F16, RD_KV_F16);
   if (rc != RD_OK) return rc;
   if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
@@ -775,8 +778,17 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   if ((rc = current_device(&dev)) != RD_OK) return rc;
   DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
   if (status == nullptr) return RD_ERR_CUDA;
+  int splits = prefill_splits(n_q, keys_total, n_head, sm_count(dev));
+  const size_t need = prefill_record_bytes(n_q, n_head, splits);
+  if (splits > 1) {
+    if (records == nullptr) {
+      records = ensure_workspace(dev, need);
+      record_bytes = records != nullptr ? need : 0;
+    }
+    if (record_bytes < need) splits = 1;   // no room: one CTA per (token tile, head) walks all keys
+  }
   return launch_prefill(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, scale, n_rot,
-                        freq_base, status, (cudaStream_t)stream);
+                        freq_base, status, (float *)records, splits, (cudaStream_t)stream);
 }
 
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
@@ -794,11 +806,19 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
                         n_rot, freq_base, stream);
 }
 
-size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int keys_total, int n_head_kv, int head_dim) {
-  if (!known_type(k_type) || !known_type(v_type) || keys_total <= 0 || n_head_kv < 1 || head_dim != kHeadDim)
-    return 0;
+// f16 copies of the caches that are not f16, then the key-split records
+static size_t prefill_copy_bytes(int k_type, int v_type, int keys_total, int n_head_kv) {
   const size_t one = align256((size_t)keys_total * n_head_kv * kHeadDim * 2);
   return (k_type != RD_KV_F16 ? one : 0) + (v_type != RD_KV_F16 ? one : 0);
+}
+size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int n_q, int keys_total, int n_head,
+                                       int n_head_kv, int head_dim) {
+  int dev;
+  if (!known_type(k_type) || !known_type(v_type) || n_q < 1 || keys_total <= 0 || n_head < 1 ||
+      n_head_kv < 1 || head_dim != kHeadDim || current_device(&dev) != RD_OK)
+    return 0;
+  return prefill_copy_bytes(k_type, v_type, keys_total, n_head_kv) +
+         align256(prefill_record_bytes(n_q, n_head, prefill_splits(n_q, keys_total, n_head, sm_count(dev))));
 }
 
 int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o, const float *gate,
@@ -810,7 +830,8 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
   if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
   if (k == nullptr || v == nullptr) return RD_ERR_NULL;
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;
-  const size_t need = rd_attn_prefill_workspace_bytes(k_type, v_type, keys_total, n_head_kv, head_dim);
+  const size_t copies = prefill_copy_bytes(k_type, v_type, keys_total, n_head_kv);
+  const size_t need = rd_attn_prefill_workspace_bytes(k_type, v_type, n_q, keys_total, n_head, n_head_kv, head_dim);
   if (need > 0) {
     if (workspace == nullptr || workspace_bytes < need) return RD_ERR_WORKSPACE;
     if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
@@ -831,8 +852,13 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
     if ((rc = launch_kv_dequant_f16(v_type, v, w, n_values, st)) != RD_OK) return rc;
     v16 = w;
   }
+  // what follows the copies holds the key-split records (never the library's own workspace:
+  // this entry allocates nothing)
+  unsigned char *rec = workspace != nullptr ? (unsigned char *)workspace + copies : nullptr;
+  static float s_dummy;   // non-null marker when no records are needed
   return prefill_common(q, k16, v16, o, gate, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
-                        n_rot, freq_base, stream);
+                        n_rot, freq_base, stream, rec != nullptr ? (void *)rec : (void *)&s_dummy,
+                        need > copies ? need - copies : 0);
 }
 
 int rd_device_status(void) {

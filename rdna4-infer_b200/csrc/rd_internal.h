@@ -139,9 +139,14 @@ int encode_f16_tmap(void *tmap_out, const void *base, int n_head_kv, int64_t n_r
 // Causal prefill attention over f16 caches on tcgen05: token i attends keys 0..pos[i]
 // (pos on the device), keys_total rows exist in the cache. gate (optional) fuses
 // out *= sigmoid(gate); n_rot > 0 applies the partial RoPE to the queries on load.
+// n_splits > 1 (with `records`, prefill_record_bytes(...) bytes): the keys are also split
+// over gridDim.z and a second launch merges the per-split records.
 int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
                    const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
-                   int n_rot, float freq_base, DeviceStatus *status, cudaStream_t st);
+                   int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits,
+                   cudaStream_t st);
+int prefill_splits(int n_q, int keys_total, int n_head, int sms);
+size_t prefill_record_bytes(int n_q, int n_head, int splits);
 
 // ---- rd_merge.cu
 // partial [n_rows][n_splits][258] -> out [n_rows][256]; optional fused sigmoid gate.

@@ -43,6 +43,7 @@
 
 #include "rd_common.cuh"
 #include "rd_internal.h"
+#include "rd_tc.cuh"
 
 // Timing experiments (skip one pipeline stage, bit mask in PrefillArgs::debug) exist only
 // in builds with -DRD_TIMING_SWITCHES; a default build compiles them out.
@@ -87,100 +88,12 @@ struct PrefillArgs {
   RopeTable rope;        // host-computed frequencies of the n_rot/2 <= 32 pairs
   int debug;             // timing experiments only (bit mask), 0 in production
   DeviceStatus *status;
+  // Split over the keys (gridDim.z > 1): CTA (tile, head, z) walks only its share of the
+  // key tiles and writes an un-normalised record (m, l, acc) per row instead of the
+  // output; prefill_merge_kernel combines the records. Fills the SMs when n_q * n_head /
+  // 128 CTAs would leave many idle.
+  float *records;        // [n_q * n_head][gridDim.z][2 + 256]
 };
-
-// ---- tcgen05 wrappers -------------------------------------------------------------
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], both behind shared-memory descriptors.
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]: the A operand lives in tensor memory (rows = lanes, two
-// f16 per 32-bit column), B behind a shared-memory descriptor.
-__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor, kind::f16: f32 accumulate, f16 A and B.
-__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
-#define RD_LD64_REGS(r)                                                                         \
-  "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),  \
-  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),       \
-  "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),     \
-  "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),     \
-  "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-// 32 lanes x 32 consecutive columns: thread i gets lane base+i, registers = columns.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
-      "%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : RD_LD64_REGS(r)
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
-      "%26,%27,%28,%29,%30,%31,%32};"
-      :
-      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
-        "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      :
-      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-        "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
-               : "memory");
-}
-
 
 // Barrier slots (8 bytes each).
 enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarX = 20,
@@ -261,7 +174,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
   const int maxpos = s_maxpos;
-  const int nt = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles this CTA walks
+  const int nt_all = maxpos >= 0 ? maxpos / kPfN + 1 : 0;  // key tiles the rows of this tile attend
+  const int jt0 = (int)(((int64_t)nt_all * blockIdx.z) / gridDim.z);        // this CTA's share of them
+  const int nt = (int)(((int64_t)nt_all * (blockIdx.z + 1)) / gridDim.z) - jt0;
 
   // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-7, 16 rows each) ----
   if (warp < 8) {
@@ -346,7 +261,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           mbar_arrive(full);
         } else {
           mbar_expect_tx(full, kPfKChunkBytes);
-          tma_load_2d(sK + slot * kPfKChunkBytes, &p.tm_k, kvh * kHeadDim + 64 * (g & 3), (g >> 2) * kPfN, full);
+          tma_load_2d(sK + slot * kPfKChunkBytes, &p.tm_k, kvh * kHeadDim + 64 * (g & 3), (jt0 + (g >> 2)) * kPfN, full);
         }
         if (++slot == kPfKSlots) {
           slot = 0;
@@ -375,7 +290,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 #pragma unroll
         for (int c = 0; c < 4; ++c)  // four [64 keys][64 dims] sub-tiles
           tma_load_2d(sV + slot * kPfVUnitBytes + c * (kPfVUnitKeys * 128), &p.tm_v, kvh * kHeadDim + 64 * c,
-                      g * kPfVUnitKeys, full);
+                      (2 * jt0 + g) * kPfVUnitKeys, full);
       }
       if (!ok) s_abort = 1;
     }
@@ -472,7 +387,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       tmem_ld32(scol, s0);
       tmem_ld32(scol + 32, s1);
       tmem_wait_ld();
-      const int key0 = j * kPfN + 64 * ch;
+      const int key0 = (jt0 + j) * kPfN + 64 * ch;
       // only tiles that reach past some row's last key need the causal mask
       if (__any_sync(0xffffffffu, key0 + 63 > my_pos)) {
 #pragma unroll
@@ -569,8 +484,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7, gt = threadIdx.x & (kPfM - 1);
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float l_tot = s_mx[0][0][r] + s_mx[0][1][r];
-    const float inv = (l_tot > 0.f && !aborted) ? 1.0f / l_tot : 0.f;
+    const bool rec_mode = gridDim.z > 1;   // un-normalised records for prefill_merge_kernel
+    const float inv = (l_tot > 0.f && !aborted) ? (rec_mode ? 1.0f : 1.0f / l_tot) : 0.f;
     const bool have = nt > 0 && !aborted;
+    if (rec_mode && ch == 0 && row0 + r < p.n_q) {
+      // header of this row's record; natural-log units like every record of the library
+      float *rec = p.records + (((size_t)(row0 + r) * p.n_head + head) * gridDim.z + blockIdx.z) * kRec;
+      const bool some = have && l_tot > 0.f;
+      rec[0] = some ? m_ref * 0.6931471805599453f : -INFINITY;
+      rec[1] = some ? l_tot : 0.f;
+    }
     const uint32_t stg = sQ + ch * (kPfM * 256);
     uint8_t *gstg = gQ + ch * (kPfM * 256);
     for (int cc = 0; cc < 2; ++cc) {
@@ -592,7 +515,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       }
       asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
       // 128 threads: 8 rows x 16 chunks per pass
-      if (p.gate == nullptr) {
+      if (rec_mode) {
+#pragma unroll 8
+        for (int pass = 0; pass < kPfM / 8; ++pass) {
+          const int rr = pass * 8 + (gt >> 4), q = gt & 15;
+          const int gr = row0 + rr;
+          if (gr < p.n_q) {
+            // a record's values start 8 bytes into a 16-byte line: two 8-byte stores
+            const float4 v = *reinterpret_cast<const float4 *>(gstg + rr * 256 + ((q ^ (rr & 15)) << 4));
+            float2 *dst = reinterpret_cast<float2 *>(
+                p.records + (((size_t)gr * p.n_head + head) * gridDim.z + blockIdx.z) * kRec + 2 + 64 * c + 4 * q);
+            dst[0] = make_float2(v.x, v.y);
+            dst[1] = make_float2(v.z, v.w);
+          }
+        }
+      } else if (p.gate == nullptr) {
 #pragma unroll 8
         for (int pass = 0; pass < kPfM / 8; ++pass) {
           const int rr = pass * 8 + (gt >> 4), q = gt & 15;
@@ -642,9 +579,78 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   }
 }
 
+// Combines the key-split records of a row: one warp-pair (64 threads, 4 dims each) per row
+// (token, head); out = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M), times sigmoid(gate)
+// if given (the gate is only read). Rows whose records are all empty give zeros.
+__global__ void __launch_bounds__(256)
+prefill_merge_kernel(const float *__restrict__ records, float *__restrict__ out, const float *__restrict__ gate,
+                     int64_t n_rows, int n_splits) {
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 6);
+  const int tx = threadIdx.x & 63;
+  if (row >= n_rows) return;
+  const float *rec = records + (size_t)row * n_splits * kRec;
+  float mm = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) mm = fmaxf(mm, rec[(size_t)z * kRec]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  if (mm != -INFINITY) {
+    for (int z = 0; z < n_splits; ++z) {
+      const float *r = rec + (size_t)z * kRec;
+      const float m = r[0];
+      if (m == -INFINITY) continue;
+      const float w = __expf(m - mm);
+      l = fmaf(r[1], w, l);
+      const float2 a = *reinterpret_cast<const float2 *>(r + 2 + 4 * tx);
+      const float2 b = *reinterpret_cast<const float2 *>(r + 4 + 4 * tx);
+      acc.x = fmaf(a.x, w, acc.x);
+      acc.y = fmaf(a.y, w, acc.y);
+      acc.z = fmaf(b.x, w, acc.z);
+      acc.w = fmaf(b.y, w, acc.w);
+    }
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  float4 o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+  if (gate != nullptr) {
+    const float4 g = *reinterpret_cast<const float4 *>(gate + (size_t)row * kHeadDim + 4 * tx);
+    o.x *= __fdividef(1.0f, 1.0f + __expf(-g.x));
+    o.y *= __fdividef(1.0f, 1.0f + __expf(-g.y));
+    o.z *= __fdividef(1.0f, 1.0f + __expf(-g.z));
+    o.w *= __fdividef(1.0f, 1.0f + __expf(-g.w));
+  }
+  *reinterpret_cast<float4 *>(out + (size_t)row * kHeadDim + 4 * tx) = o;
+}
+
+// Key splits that fill the GPU, picked with a three-constant cost model measured on B200:
+// a key tile costs a CTA about 2 us, a CTA's prologue + epilogue about 9 us (the query
+// tile is converted and the result written whatever the key count), and the records cost
+// about 0.5 ns each (written by the tile kernel, read by the merge pass). Splitting pays only when the waves it saves outweigh the fixed
+// costs it multiplies: 512 tokens x 24 heads gain from about 8192 keys upwards (3 splits:
+// 96 -> 288 CTAs = two full waves of 148 SMs), shorter prefixes do not.
+int prefill_splits(int n_q, int keys_total, int n_head, int sms) {
+  const int ctas = ((n_q + kPfM - 1) / kPfM) * n_head;
+  const int tiles = (keys_total + kPfN - 1) / kPfN;
+  auto cost = [&](int z) {
+    const double waves = (double)((ctas * z + sms - 1) / sms);
+    return waves * ((double)tiles / z * 2.0 + 9.0) + (z > 1 ? 0.0005 * n_q * n_head * z : 0.0);
+  };
+  int best = 1;
+  double best_cost = cost(1) * 0.92;   // a split must win clearly to be worth its records
+  for (int z = 2; z <= 8 && tiles / z >= 8; ++z) {
+    if (cost(z) < best_cost) {
+      best_cost = cost(z);
+      best = z;
+    }
+  }
+  return best;
+}
+size_t prefill_record_bytes(int n_q, int n_head, int splits) {
+  return splits > 1 ? (size_t)n_q * n_head * splits * kRec * sizeof(float) : 0;
+}
+
 int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
                    const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
-                   int n_rot, float freq_base, DeviceStatus *status, cudaStream_t st) {
+                   int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits,
+                   cudaStream_t st) {
   PrefillArgs a;
   memset(&a, 0, sizeof(a));
   int rc = encode_f16_tmap(&a.tm_k, k, n_head_kv, keys_total, kPfN);
@@ -676,9 +682,17 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
       return RD_ERR_CUDA;
     if (dev >= 0 && dev < 32) attr_set[dev] = true;
   }
-  const dim3 grid((unsigned)((n_q + kPfM - 1) / kPfM), (unsigned)n_head);
+  if (n_splits < 1 || records == nullptr) n_splits = 1;
+  a.records = records;
+  const dim3 grid((unsigned)((n_q + kPfM - 1) / kPfM), (unsigned)n_head, (unsigned)n_splits);
   prefill_kernel<<<grid, kPfThreads, kPfSmemBytes, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+  if (n_splits > 1) {
+    const int64_t n_rows = (int64_t)n_q * n_head;
+    prefill_merge_kernel<<<(unsigned)((n_rows + 3) / 4), 256, 0, st>>>(records, out, gate, n_rows, n_splits);
+    if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+  }
+  return RD_OK;
 }
 
 }  // namespace rd

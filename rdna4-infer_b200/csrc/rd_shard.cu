@@ -7,15 +7,16 @@
 //   header   epoch, arrival counter
 //   records  [parity][source rank][head][dim quarter][2 + 64] 8-byte words, each word =
 //            (f32 value, epoch it belongs to): m, l and 64 accumulator values
-// One sharded attention call on rank r is two launches on r's stream:
-//   1. the split-KV decode kernel over r's slice of the keys -> S records per head in
-//      the caller's workspace (rd_decode.cuh);
-//   2. shard_exchange_kernel<PUSH, MERGE>: CTA (head, quarter) reduces the S records to
-//      one and STORES ITS QUARTER INTO EVERY RANK'S buffer, every value as one 8-byte
-//      (value, epoch) store; the same CTA then reads the `world` parts from its own
-//      buffer, each thread spinning (bounded) on its own words until they carry this
-//      call's epoch, and merges them into its quarter of the output (optional fused
-//      sigmoid gate). The last CTA to finish advances the local epoch.
+// One sharded attention call on rank r is ONE launch on r's stream (rd_attn_decode_sharded):
+// the split-KV decode kernel over r's slice of the keys writes S records per head into the
+// caller's workspace (rd_decode.cuh); every CTA then reports in, and the launch's first
+// n_head * 4 CTAs take one (head, dim quarter) each: wait (bounded) for all CTAs, reduce the
+// S records to one part, STORE IT INTO EVERY RANK'S buffer, every value as one 8-byte
+// (value, epoch) store, then read the `world` parts from their own buffer, each thread
+// spinning (bounded) on its own words until they carry this call's epoch, and merge them
+// into the output quarter (optional fused sigmoid gate). The last of them advances the local
+// epoch. The same two halves exist as the kernel below for callers that compute the
+// records themselves: shard_exchange_kernel<PUSH, MERGE>, grid (head, quarter).
 // Tagging every word with the epoch (the low-latency protocol of collective libraries)
 // needs no flag, no fence and no barrier between data and flag: an 8-byte store arrives
 // whole, so a word that shows the epoch IS the value. Measured on two B200s, a system

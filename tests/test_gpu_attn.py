@@ -272,3 +272,32 @@ def test_long_context_q4_0_full_size(G, oracle, rd):
     p = G.host(part)
     assert np.isneginf(p[:, :, 0]).all() and (p[:, :, 1:] == 0).all()
     G.status_ok()
+
+
+def test_long_context_q4_0_full_size_normal_rows(G, oracle, rd):
+    """The headline shape as the benchmark config words it: 131001 keys of seeded N(0,1) f32
+    rows QUANTIZED BY THE KV-APPEND KERNEL into q4_0 caches (position 131000 last), then the
+    decode kernel, against the oracle's attention over the bytes the append kernel wrote --
+    and those bytes against the oracle's quantizer on a sample of rows."""
+    import torch
+    n = 131001
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    K = torch.randn(n, 4, 256, generator=gen, device="cuda")
+    V = torch.randn(n, 4, 256, generator=gen, device="cuda")
+    q = torch.randn(24, 256, generator=gen, device="cuda")
+    kc = torch.empty(n * 4 * 144, dtype=torch.uint8, device="cuda")
+    vc = torch.empty_like(kc)
+    rd.check(rd.lib.rd_kv_append(3, 3, rd.ptr(K), rd.ptr(V), rd.ptr(kc), rd.ptr(vc), n, 4, 256, None, 0, 0.0,
+                                 G.st()))
+    out = G.poison((24, 256))
+    rd.check(rd.lib.rd_attn_decode(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(out), n - 1, 24, 4, 256, 1 / 16,
+                                   3, 3, G.st()))
+    torch.cuda.synchronize()
+    hk, hv = G.host(kc), G.host(vc)
+    rows = np.r_[0:64, 65000:65064, n - 64:n]          # bytes: first, middle and last rows
+    want_rows = oracle.kv_store_rows(3, G.host(K[rows]))
+    got_rows = hk.reshape(n, 4 * 144)[rows].reshape(-1)
+    assert (want_rows == got_rows).all()
+    want = oracle.attn(G.host(q)[None], hk, hv, [n - 1], 4, 1 / 16, 3, 3)[0]
+    check_attn(G.host(out), want, what="131001 keys q4_0 of N(0,1) rows")
+    G.status_ok()
