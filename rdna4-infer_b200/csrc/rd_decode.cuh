@@ -1189,6 +1189,19 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
 }
 #undef RD_TRACE
 
+#ifdef RD_TIMING_SWITCHES
+}  // namespace rd
+// Experimental tensor-memory flavour of the kernel (tcgen05.mma with the dequantized
+// fragments in TMEM): correct, slower than this kernel so far, built only into
+// timing-switch builds and taken there with RD_TC_DECODE=1.
+#include "rd_decode_tc.cuh"
+namespace rd {
+inline bool tc_decode_enabled() {
+  const char *e = getenv("RD_TC_DECODE");
+  return e != nullptr && atoi(e) != 0;
+}
+#endif
+
 // Shared-memory plan of one (KT, VT) instantiation and the opt-in for it.
 template <int KT, int VT, bool MULTI>
 int prepare_decode(int n_head_kv, int *depth_out, int *group_bytes_out, size_t *smem_out) {
@@ -1268,6 +1281,13 @@ int launch_decode_typed(const DecodeArgs &a, cudaStream_t st) {
     k.x_out = a.push_out;
     k.x_gate = a.push_gate;
   }
+#ifdef RD_TIMING_SWITCHES
+  if constexpr (tc_decode_usable(KT, VT)) {
+    if (tc_decode_enabled() && a.n_head_kv == 4 && a.n_tok == 1 && k.k_tmap && k.v_tmap && a.push == nullptr &&
+        a.k_new == nullptr)
+      return launch_decode_tc<KT, VT>(k, a.n_splits, st);
+  }
+#endif
   const dim3 grid((unsigned)a.n_splits, (unsigned)a.n_tok);
   return launch_pdl(2, decode_kernel<KT, VT, false>, grid, dim3(4 * G * 32), smem, st, k) == cudaSuccess
              ? RD_OK
