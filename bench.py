@@ -548,6 +548,13 @@ def main():
                                                 NKV, HD, SCALE, KT, VT, rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
                                                 st))
             return 2
+        if owns_new_row and world > 1 and group is not None:   # the owner: append + decode + exchange, one launch
+            rd.check(L.rd_attn_decode_sharded_append(rd.ptr(q_dev[l]), rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
+                                                     rd.ptr(kcache[l]), rd.ptr(vcache[l]), rd.ptr(o_dev[l]),
+                                                     slice_rows - 1, NH, NKV, HD, SCALE, KT, VT,
+                                                     rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
+                                                     ctypes.addressof(group), st))
+            return 1
         if owns_new_row:
             off = (POS - kb) * NKV * row
             rd.check(L.rd_kv_append(KT, VT, rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
@@ -564,7 +571,7 @@ def main():
                                               rd.ptr(o_dev[l]), slice_rows - 1, NH, NKV, HD, SCALE, KT, VT,
                                               rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
                                               ctypes.addressof(group), st))
-            n += 3
+            n += 1
         else:
             rd.check(L.rd_attn_decode_ws(rd.ptr(q_dev[l]), rd.ptr(kcache[l]), rd.ptr(vcache[l]), None,
                                          rd.ptr(rec_mine), 0, slice_rows - 1, NH, NKV, HD, SCALE, KT, VT, 1,

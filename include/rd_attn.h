@@ -266,6 +266,15 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
                            int n_head, int n_head_kv, int head_dim, float scale, int k_type,
                            int v_type, float *gate, void *workspace, size_t workspace_bytes,
                            const rd_shard_group *group, void *stream);
+/* The same for the rank that owns the newest position: k_new / v_new [n_head_kv][head_dim]
+ * f32 are quantized and stored as row t of its slice inside the launch (bytes as
+ * rd_kv_append writes them; rotate K beforehand if the model does), and that key joins the
+ * exchange as one more record -- rd_kv_append (kv_store_row_launch, include/rdna4/kv.h:
+ * 673-694) and rd_attn_decode_sharded in one launch. q must not alias out. */
+int rd_attn_decode_sharded_append(const float *q, const float *k_new, const float *v_new, void *k, void *v,
+                                  float *out, int t, int n_head, int n_head_kv, int head_dim, float scale,
+                                  int k_type, int v_type, float *gate, void *workspace,
+                                  size_t workspace_bytes, const rd_shard_group *group, void *stream);
 int rd_attn_shard_push(const float *partial, int n_splits, int n_head, int head_dim,
                        const rd_shard_group *group, void *stream);
 int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,

@@ -57,6 +57,8 @@ SIGNATURES = {
     "rd_shard_xbuf_bytes": (C.c_size_t, [_I, _I, _I]),
     "rd_attn_decode_sharded": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, C.c_size_t,
                                     _P, _P]),
+    "rd_attn_decode_sharded_append": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, C.c_size_t,
+                                           _P, _P]),
     "rd_attn_shard_push": (_I, [_P, _I, _I, _I, _P, _P]),
     "rd_attn_shard_merge": (_I, [_P, _P, _I, _I, _P, _P]),
     "rd_attn_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P]),

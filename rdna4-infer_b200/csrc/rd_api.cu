@@ -685,10 +685,37 @@ int rd_attn_shard_merge(float *out, float *gate, int n_head, int head_dim,
   return launch_shard_merge(out, gate, n_head, g, status, (cudaStream_t)stream);
 }
 
+// k_new / v_new != NULL: the rank that owns the newest position; row t of its slice is
+// stored by the same launch and joins the exchange as one more record.
+static int decode_sharded(const float *q, const float *k_new, const float *v_new, const void *k, const void *v,
+                          float *out, int t, int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                          int v_type, float *gate, void *workspace, size_t workspace_bytes,
+                          const rd_shard_group *group, void *stream);
+
 int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *out, int t,
                            int n_head, int n_head_kv, int head_dim, float scale, int k_type,
                            int v_type, float *gate, void *workspace, size_t workspace_bytes,
                            const rd_shard_group *group, void *stream) {
+  return decode_sharded(q, nullptr, nullptr, k, v, out, t, n_head, n_head_kv, head_dim, scale, k_type, v_type,
+                        gate, workspace, workspace_bytes, group, stream);
+}
+
+int rd_attn_decode_sharded_append(const float *q, const float *k_new, const float *v_new, void *k, void *v,
+                                  float *out, int t, int n_head, int n_head_kv, int head_dim, float scale,
+                                  int k_type, int v_type, float *gate, void *workspace,
+                                  size_t workspace_bytes, const rd_shard_group *group, void *stream) {
+  if (k_new == nullptr || v_new == nullptr) return RD_ERR_NULL;
+  if (t < 0) return RD_ERR_SHAPE;
+  if (q == out) return RD_ERR_UNSUPPORTED;   // the exchange reads whole query rows while it writes out
+  if (!aligned(k_new, 4) || !aligned(v_new, 4)) return RD_ERR_ALIGN;
+  return decode_sharded(q, k_new, v_new, k, v, out, t, n_head, n_head_kv, head_dim, scale, k_type, v_type, gate,
+                        workspace, workspace_bytes, group, stream);
+}
+
+static int decode_sharded(const float *q, const float *k_new, const float *v_new, const void *k, const void *v,
+                          float *out, int t, int n_head, int n_head_kv, int head_dim, float scale, int k_type,
+                          int v_type, float *gate, void *workspace, size_t workspace_bytes,
+                          const rd_shard_group *group, void *stream) {
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
   if (rc != RD_OK) return rc;
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return RD_ERR_NULL;
@@ -702,9 +729,16 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
   if ((rc = current_device(&dev)) != RD_OK) return rc;
   DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
   if (status == nullptr) return RD_ERR_CUDA;
+  // with a fused append the split-KV loop attends keys 0..t-1; row t joins in the exchange
+  const int t_loop = k_new != nullptr ? t - 1 : t;
   const int tile = decode_tile_keys(k_type, v_type);
-  const int64_t tiles = ((int64_t)t + tile) / tile;  // ceil((t + 1) / tile); 0 for an empty slice
-  const int S = plan_splits(sm_count(dev), 1, tiles);
+  const int64_t tiles = ((int64_t)t_loop + tile) / tile;  // ceil((t_loop + 1) / tile); 0 for an empty slice
+  // The exchange runs as n_head * 4 roles on the launch's first CTAs: a short slice still
+  // gets that many CTAs (the ones without keys write empty records) instead of a few CTAs
+  // walking the roles one after another.
+  int S = plan_splits(sm_count(dev), 1, tiles);
+  const int roles = std::min(n_head * (head_dim / 64), sm_count(dev));
+  if (S < roles) S = roles;
   if (workspace_bytes < partial_floats(1, n_head, S) * sizeof(float)) return RD_ERR_WORKSPACE;
   DecodeArgs a;
   a.q = q;
@@ -712,7 +746,10 @@ int rd_attn_decode_sharded(const float *q, const void *k, const void *v, float *
   a.v = v;
   a.partial = (float *)workspace;
   a.pos = nullptr;
-  a.t = t;
+  a.t = t_loop;
+  a.k_new = k_new;
+  a.v_new = v_new;
+  a.new_row = t;
   a.key_begin = 0;
   a.n_tok = 1;
   a.n_head = n_head;

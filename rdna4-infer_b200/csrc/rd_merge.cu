@@ -16,41 +16,6 @@ namespace rd {
 constexpr int kMergeDims = 64;    // dims per CTA
 constexpr int kMergeGroups = 16;  // record groups per CTA
 
-// One stored value of a cache row (kv_load, include/rdna4/kv.h:174-229), type chosen at run
-// time: used for the single newest key the merge can fold in (see MODE 3).
-__device__ __forceinline__ float load_cache_value(const uint8_t *row, int type, int d) {
-  const int b = d >> 5, j = d & 31;
-  auto h2f = [](const uint8_t *p) { return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p))); };
-  switch (type) {
-    case RD_KV_F32: return reinterpret_cast<const float *>(row)[d];
-    case RD_KV_F16: return h2f(row + 2 * d);
-    case RD_KV_Q8_0: {
-      const uint8_t *blk = row + 34 * b;
-      return __fmul_rn(h2f(blk), (float)(int8_t)blk[2 + j]);
-    }
-    case RD_KV_Q4_0: {
-      const uint8_t *blk = row + 18 * b;
-      const int byte = blk[2 + (j & 15)];
-      return __fmul_rn(h2f(blk), (float)((j < 16 ? (byte & 15) : (byte >> 4)) - 8));
-    }
-    case RD_KV_Q5_0: {
-      const uint8_t *blk = row + 22 * b;
-      const int byte = blk[6 + (j & 15)];
-      const int hi = (blk[2 + (j >> 3)] >> (j & 7)) & 1;
-      return __fmul_rn(h2f(blk), (float)(((j < 16 ? (byte & 15) : (byte >> 4)) | (hi << 4)) - 16));
-    }
-    default: {  // RD_KV_Q4_1
-      const uint8_t *blk = row + 20 * b;
-      const int byte = blk[4 + (j & 15)];
-      return __fadd_rn(__fmul_rn(h2f(blk), (float)(j < 16 ? (byte & 15) : (byte >> 4))), h2f(blk + 2));
-    }
-  }
-}
-__host__ __device__ constexpr int merge_row_bytes(int type) {
-  return type == RD_KV_F32 ? 1024 : type == RD_KV_F16 ? 512 : type == RD_KV_Q8_0 ? 272 : type == RD_KV_Q4_0 ? 144
-         : type == RD_KV_Q5_0 ? 176 : 160;
-}
-
 // MODE 0: normalised output (optionally gated). MODE 1: un-normalised record out.
 // MODE 3: like 0, plus one more key -- the newest position's row, still only in the cache
 // -- attended here as one more record (m = scale * q.k, l = 1, acc = v).

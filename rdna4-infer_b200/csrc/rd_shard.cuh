@@ -119,24 +119,6 @@ __device__ __forceinline__ void shard_push_part(const float *partial, int n_in, 
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(NG * kPushDims) : "memory");   // the arrays may be reused
 }
 
-// Spins until the word carries `epoch`; false when wait_ns ran out first. The clock is
-// only consulted every 64 polls: reading it costs as much as a poll.
-__device__ __forceinline__ bool wait_word(const uint2 *p, uint32_t epoch, unsigned long long wait_ns,
-                                          float &value) {
-  uint2 w = ld_word_sys(p);
-  if (w.y != epoch) {
-    const unsigned long long t0 = global_ns();
-    unsigned polls = 0;
-    do {
-      if ((++polls & 63u) == 0 && global_ns() - t0 > wait_ns) return false;
-      w = ld_word_sys(p);
-    } while (w.y != epoch);
-  }
-  value = __uint_as_float(w.x);
-  return true;
-}
-
-
 // MERGE of one (head row, dim quarter) by 64 threads (tx = dim of the quarter; whole warps):
 // waits (bounded) for every rank's part of this call in the LOCAL buffer, combines them and
 // writes the output quarter, with the optional fused sigmoid gate (sigmoid stored back).
@@ -149,16 +131,49 @@ __device__ __forceinline__ void shard_merge_part(float *out, float *gate, int n_
   const size_t rstride = (size_t)n_head * kQuarters * kXPart;
   const size_t part0 = (size_t)par * g.world * rstride + ((size_t)row * kQuarters + quarter) * kXPart;
   const uint2 *recs = xwords(g.x[g.rank]) + part0;
+  // the gate value does not depend on the exchange: requested before the waits
+  float *gp = gate != nullptr ? gate + (size_t)row * kHeadDim + d : nullptr;
+  const float gv = gp != nullptr ? *gp : 0.f;
   bool ok = true;
   float m_r[kShardMaxWorld], l_r[kShardMaxWorld], a_r[kShardMaxWorld];
+  // Every round requests all 3 * world words back to back (one round trip to L2 for the
+  // lot, not one per word) and repeats until each carries this call's epoch, or the time
+  // limit passes (the clock is read every 64 rounds: it costs as much as a round).
 #pragma unroll
   for (int r = 0; r < kShardMaxWorld; ++r) {
     m_r[r] = -INFINITY;
     l_r[r] = a_r[r] = 0.f;
-    if (r < g.world && ok) {
-      const uint2 *rec = recs + r * rstride;
-      ok = wait_word(rec, epoch, g.wait_ns, m_r[r]) && wait_word(rec + 1, epoch, g.wait_ns, l_r[r]) &&
-           wait_word(rec + 2 + tx, epoch, g.wait_ns, a_r[r]);
+  }
+  unsigned long long t0 = 0;
+  unsigned polls = 0;
+  for (;;) {
+    uint2 w_m[kShardMaxWorld], w_l[kShardMaxWorld], w_a[kShardMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kShardMaxWorld; ++r) {
+      if (r < g.world) {
+        const uint2 *rec = recs + r * rstride;
+        w_m[r] = ld_word_sys(rec);
+        w_l[r] = ld_word_sys(rec + 1);
+        w_a[r] = ld_word_sys(rec + 2 + tx);
+      }
+    }
+    bool all = true;
+#pragma unroll
+    for (int r = 0; r < kShardMaxWorld; ++r) {
+      if (r < g.world) {
+        all = all && w_m[r].y == epoch && w_l[r].y == epoch && w_a[r].y == epoch;
+        m_r[r] = __uint_as_float(w_m[r].x);
+        l_r[r] = __uint_as_float(w_l[r].x);
+        a_r[r] = __uint_as_float(w_a[r].x);
+      }
+    }
+    if (all) break;
+    if ((++polls & 63u) == 0) {
+      if (t0 == 0) t0 = global_ns();
+      else if (global_ns() - t0 > g.wait_ns) {
+        ok = false;
+        break;
+      }
     }
   }
   ok = __all_sync(0xffffffffu, ok);
@@ -179,9 +194,8 @@ __device__ __forceinline__ void shard_merge_part(float *out, float *gate, int n_
     }
   }
   float o = (ok && mm != -INFINITY && l > 0.f) ? a / l : 0.f;
-  if (gate != nullptr) {
-    float *gp = gate + (size_t)row * kHeadDim + d;
-    const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
+  if (gp != nullptr) {
+    const float sg = __fdiv_rn(1.0f, 1.0f + expf(-gv));
     *gp = sg;
     o *= sg;
   }
@@ -193,10 +207,15 @@ __device__ __forceinline__ void shard_merge_part(float *out, float *gate, int n_
 // quarter and its group's records ty, ty + NG, ... -- all of them requested before the
 // first is used, so the walk over a launch's ~150 records is ONE round trip to L2. Scratch:
 // s_acc [NG][64] floats, s_l [NG], s_gm [NG]. All NT threads call it.
+// xv != nullptr folds one more key in as a record of its own (m = x_score in natural-log
+// units, l = 1, acc = the key's stored V row xv of type xvt): the newest position's row,
+// which the same launch has just stored and none of its CTAs attended.
 template <int NT>
 __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n_in, int n_head, int row,
                                                      int quarter, const ShardPeers &g, uint32_t epoch,
-                                                     float *s_acc, float *s_l, float *s_gm, int bar_id) {
+                                                     float *s_acc, float *s_l, float *s_gm, int bar_id,
+                                                     float x_score = 0.f, const uint8_t *xv = nullptr,
+                                                     int xvt = 0) {
   constexpr int NG = NT / 16;
   constexpr int kBatch = 8;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -262,6 +281,13 @@ __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n
         a = fmaf(s_acc[i * kPushDims + dx], w, a);
         l = fmaf(s_l[i], w, l);
       }
+    }
+    if (xv != nullptr) {
+      const float mx = fmaxf(mm, x_score);
+      const float f = mm == -INFINITY ? 0.f : expf(mm - mx), w = expf(x_score - mx);
+      a = fmaf(load_cache_value(xv, xvt, quarter * kPushDims + dx), w, a * f);
+      l = fmaf(l, f, w);
+      mm = mx;
     }
     const int par = epoch & 1;
     const size_t rstride = (size_t)n_head * kQuarters * kXPart;

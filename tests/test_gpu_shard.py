@@ -99,6 +99,50 @@ def test_world_one_sharded_entry_equals_decode(G, oracle):
     G.status_ok()
 
 
+@pytest.mark.parametrize("kt,vt,n", [(3, 3, 3000), (2, 1, 1), (0, 0, 517), (4, 5, 2), (1, 3, 9000)])
+def test_world_one_sharded_append_stores_the_row_and_attends_it(G, oracle, kt, vt, n):
+    """rd_attn_decode_sharded_append = rd_kv_append of row n-1 + rd_attn_decode_sharded over
+    n keys, in one launch: the stored bytes are the oracle's, the output attends the new
+    key. n = 1 is the owner of an otherwise empty slice."""
+    import ctypes as C
+    rd, lib = G.rd, G.lib
+    rng = np.random.default_rng(40 + n)
+    K = rng.standard_normal((n, NKV, HD)).astype(np.float32)
+    V = rng.standard_normal((n, NKV, HD)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(kt, K), oracle.kv_store_rows(vt, V)
+    rk, rv = rd.row_bytes(kt) * NKV, rd.row_bytes(vt) * NKV
+    k0, v0 = kc.copy(), vc.copy()
+    k0[(n - 1) * rk:], v0[(n - 1) * rv:] = 0xEE, 0xEE     # the newest row is not in the cache yet
+    bufs, groups = make_groups(G, 1)
+    dk, dv = G.dev(k0), G.dev(v0)
+    nbytes = lib.rd_attn_workspace_bytes(1, NH, HD)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    for call in range(2):
+        q = rng.standard_normal((NH, HD)).astype(np.float32)
+        gate = rng.standard_normal((NH, HD)).astype(np.float32)
+        want_g, want = oracle.sigmoid_gate(gate.copy(), oracle.attn(q[None], kc, vc, [n - 1], NKV, 1 / 16, kt, vt)[0])
+        dq, dg, out = G.dev(q), G.dev(gate), G.poison((NH, HD))
+        dkn, dvn = G.dev(K[n - 1]), G.dev(V[n - 1])
+        rd.check(lib.rd_attn_decode_sharded_append(rd.ptr(dq), rd.ptr(dkn), rd.ptr(dvn), rd.ptr(dk), rd.ptr(dv),
+                                                   rd.ptr(out), n - 1, NH, NKV, HD, 1 / 16, kt, vt, rd.ptr(dg),
+                                                   rd.ptr(ws), nbytes, C.addressof(groups[0]), G.st()))
+        torch.cuda.synchronize()
+        assert np.array_equal(G.host(dk), kc) and np.array_equal(G.host(dv), vc)
+        check_attn(G.host(out), want, what=f"call {call}")
+        assert np.abs(G.host(dg) - want_g).max() <= 1e-6
+    G.status_ok()
+    # argument errors of the fused form
+    assert lib.rd_attn_decode_sharded_append(rd.ptr(dq), None, rd.ptr(dvn), rd.ptr(dk), rd.ptr(dv), rd.ptr(out),
+                                             n - 1, NH, NKV, HD, 1 / 16, kt, vt, None, rd.ptr(ws), nbytes,
+                                             C.addressof(groups[0]), G.st()) == rd.ERR_NULL
+    assert lib.rd_attn_decode_sharded_append(rd.ptr(dq), rd.ptr(dkn), rd.ptr(dvn), rd.ptr(dk), rd.ptr(dv),
+                                             rd.ptr(out), -1, NH, NKV, HD, 1 / 16, kt, vt, None, rd.ptr(ws), nbytes,
+                                             C.addressof(groups[0]), G.st()) == rd.ERR_SHAPE
+    assert lib.rd_attn_decode_sharded_append(rd.ptr(dq), rd.ptr(dkn), rd.ptr(dvn), rd.ptr(dk), rd.ptr(dv),
+                                             rd.ptr(dq), n - 1, NH, NKV, HD, 1 / 16, kt, vt, None, rd.ptr(ws),
+                                             nbytes, C.addressof(groups[0]), G.st()) == rd.ERR_UNSUPPORTED
+
+
 def test_missing_rank_times_out_and_reports(G):
     """A rank that never pushes: the merge gives up after the wait limit, stores zeros,
     and the library reports RD_ERR_DEVICE once; the context stays usable."""

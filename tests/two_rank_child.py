@@ -42,8 +42,12 @@ def main():
         rk, rv = rd.row_bytes(kt) * NKV, rd.row_bytes(vt) * NKV
         per = (n_keys + world - 1) // world
         b, e = rank * per, min(n_keys, (rank + 1) * per)
-        dk = torch.from_numpy(kc[b * rk:max(e, b + 1) * rk].copy()).cuda()
-        dv = torch.from_numpy(vc[b * rv:max(e, b + 1) * rv].copy()).cuda()
+        owner = b < n_keys <= e                                 # this rank's slice ends with the newest key
+        ks, vs = kc[b * rk:max(e, b + 1) * rk].copy(), vc[b * rv:max(e, b + 1) * rv].copy()
+        if owner:                                               # ... which its fused append stores
+            ks[-rk:], vs[-rv:] = 0xEE, 0xEE
+        dk, dv = torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda()
+        dkn, dvn = torch.from_numpy(K[n_keys - 1]).cuda(), torch.from_numpy(V[n_keys - 1]).cuda()
         wsb = lib.rd_attn_workspace_bytes(1, NH, HD)
         ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
         for call in range(3):                                   # both parities of the buffer, and reuse
@@ -53,11 +57,20 @@ def main():
             want_g, want = ora.sigmoid_gate(gate.copy(), y)
             dq, dg = torch.from_numpy(q).cuda(), torch.from_numpy(gate).cuda()
             out = torch.full((NH, HD), float("nan"), device="cuda")
-            rc = lib.rd_attn_decode_sharded(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), e - b - 1, NH, NKV, HD,
-                                            1 / 16, kt, vt, rd.ptr(dg), rd.ptr(ws), wsb, C.addressof(group),
-                                            rd.stream_ptr())
+            if owner:
+                rc = lib.rd_attn_decode_sharded_append(rd.ptr(dq), rd.ptr(dkn), rd.ptr(dvn), rd.ptr(dk), rd.ptr(dv),
+                                                       rd.ptr(out), e - b - 1, NH, NKV, HD, 1 / 16, kt, vt,
+                                                       rd.ptr(dg), rd.ptr(ws), wsb, C.addressof(group),
+                                                       rd.stream_ptr())
+            else:
+                rc = lib.rd_attn_decode_sharded(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), e - b - 1, NH, NKV,
+                                                HD, 1 / 16, kt, vt, rd.ptr(dg), rd.ptr(ws), wsb, C.addressof(group),
+                                                rd.stream_ptr())
             assert rc == rd.OK, rc
             torch.cuda.synchronize()
+            if owner:
+                assert np.array_equal(dk.cpu().numpy()[-rk:], kc[(n_keys - 1) * rk:n_keys * rk])
+                assert np.array_equal(dv.cpu().numpy()[-rv:], vc[(n_keys - 1) * rv:n_keys * rv])
             got = out.cpu().numpy()
             err = float(np.abs(got - want).max())
             cos = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
