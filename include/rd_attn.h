@@ -369,6 +369,10 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
  * library on the current device gave up on a bounded wait since the last call.
  * Synchronises the device; meant for tests and debugging, not for the hot path. */
 int rd_device_status(void);
+/* Which wait gave up, for the last RD_ERR_DEVICE that rd_device_status returned: a small
+ * site number from the kernel sources (prefill 11-22, decode 1-9 and 90, exchange 100 +
+ * rank); 0 if none was ever reported. For bug reports. */
+int rd_device_timeout_site(void);
 
 /* Library identification ("rd_attn_b200 <version> sm_100a"). */
 const char *rd_version(void);

@@ -72,6 +72,7 @@ SIGNATURES = {
     "rd_attn_prefill_typed": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P,
                                    C.c_size_t, _P]),
     "rd_device_status": (_I, []),
+    "rd_device_timeout_site": (_I, []),
 }
 
 

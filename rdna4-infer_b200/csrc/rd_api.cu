@@ -898,6 +898,8 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
                         need > copies ? need - copies : 0);
 }
 
+static int g_last_site = 0;   // `where` of the last time-out rd_device_status reported
+
 int rd_device_status(void) {
   int dev;
   int rc = current_device(&dev);
@@ -908,10 +910,13 @@ int rd_device_status(void) {
   DeviceStatus h;
   if (cudaMemcpy(&h, st, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return RD_ERR_CUDA;
   if (h.timeout_flag != 0) {
+    g_last_site = h.where;
     cudaMemset(st, 0, sizeof(h));
     return RD_ERR_DEVICE;
   }
   return RD_OK;
 }
+
+int rd_device_timeout_site(void) { return g_last_site; }
 
 }  // extern "C"

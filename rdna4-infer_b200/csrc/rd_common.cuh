@@ -185,6 +185,25 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
+// Packed pairs of f32 (sm_100 add.f32x2 / fma.rn.f32x2: two lanes per instruction).
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 // D = A(16x16, row) * B(16x8, col) + D, f16 inputs, f32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -223,9 +242,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitLimit polls, records the site in `status` and
-// returns false so the caller can unwind without leaving the GPU spinning.
-constexpr uint32_t kWaitLimit = 4u << 20;
+// Bounded wait: gives up once kWaitNs of wall-clock time have passed (the clock is read
+// every 256 polls), records the site in `status` and returns false so the caller can
+// unwind without leaving the GPU spinning.
+constexpr unsigned long long kWaitNs = 2000000000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -241,11 +266,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, DeviceS
                                           int site) {
   // a short burst of non-suspending polls first: most waits in a running pipeline are
   // satisfied within a few hundred cycles, and try_wait may park the thread for longer
-  for (int i = 0; i < 128; ++i) {
+#ifndef RD_POLL_BURST
+#define RD_POLL_BURST 128
+#endif
+  for (int i = 0; i < RD_POLL_BURST; ++i) {
     if (mbar_test_wait(bar, parity)) return true;
   }
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+  const unsigned long long t0 = global_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0 && global_ns() - t0 > kWaitNs) break;
   }
   if (status != nullptr && atomicExch(&status->timeout_flag, 1) == 0) status->where = site;
   return false;

@@ -8,7 +8,7 @@
 //                     over the first 64 columns of its buffer (the A operand of O += P V,
 //                     read from TMEM)
 // Shared memory (224 KB): Q as f16 in the K-major 128-byte-swizzled layout (64 KB), a ring
-// of six K chunks of [128 keys][64 dims] (96 KB) and a ring of two V units of 64 keys
+// of three K units of [128 keys][128 dims] (96 KB) and a ring of two V units of 64 keys
 // (64 KB), all filled by TMA with the hardware 128B swizzle.
 //
 //   prologue   the 128 x 256 f32 query rows -> optional partial RoPE, scale*log2(e), f16,
@@ -49,8 +49,16 @@
 // in builds with -DRD_TIMING_SWITCHES; a default build compiles them out.
 #ifdef RD_TIMING_SWITCHES
 #define RD_PF_DEBUG(p) ((p).debug)
+// phase trace of CTA (0, 0, 0): [role 0..3][tile 0..47][point 0..7] clock64 values
+__device__ unsigned long long g_pf_trace[4][48][8];
+#define RD_PF_TRACE(role, j, pt)                                                              \
+  do {                                                                                        \
+    if ((p.debug & 64) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 48)  \
+      g_pf_trace[role][j][pt] = clock64();                                                    \
+  } while (0)
 #else
 #define RD_PF_DEBUG(p) 0
+#define RD_PF_TRACE(role, j, pt) do { } while (0)
 #endif
 
 namespace rd {
@@ -59,12 +67,13 @@ constexpr int kPfM = 128;                 // query rows per CTA
 constexpr int kPfN = 128;                 // keys per tile
 constexpr int kPfQBytes = kPfM * kHeadDim * 2;             // 65536 (also the epilogue staging)
 constexpr int kPfKChunkBytes = kPfN * 128;                 // [128 keys][64 dims] f16: 16384
-constexpr int kPfKSlots = 6;                               // 1.5 tiles of K in flight
+constexpr int kPfKUnitBytes = 2 * kPfKChunkBytes;          // K unit: [128 keys][128 dims], two chunks
+constexpr int kPfKSlots = 3;                               // 1.5 tiles of K in flight
 constexpr int kPfVUnitKeys = 64;
 constexpr int kPfVUnitBytes = kPfVUnitKeys * kHeadDim * 2; // 32768
 constexpr int kPfVSlots = 2;
 // 224 KB of dynamic shared memory + < 3 KB static = the 227 KB an sm_100 CTA may use
-constexpr int kPfSmemBytes = kPfQBytes + kPfKSlots * kPfKChunkBytes + kPfVSlots * kPfVUnitBytes;
+constexpr int kPfSmemBytes = kPfQBytes + kPfKSlots * kPfKUnitBytes + kPfVSlots * kPfVUnitBytes;
 constexpr int kPfThreads = 384;           // 8 softmax warps, K TMA, S MMA, V TMA, PV MMA warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 0;            // columns [0, 256): output accumulator
@@ -96,8 +105,8 @@ struct PrefillArgs {
 };
 
 // Barrier slots (8 bytes each).
-enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarX = 20,
-       kBarO = 22, kBarQ = 24, kBarCount = 25 };
+enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarO = 20,
+       kBarQ = 22, kBarR = 23, kBarCount = 31 };   // kBarR: [warp pair 0..3][tile parity]
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -106,7 +115,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   __shared__ int s_maxpos;
   __shared__ int s_abort;
   __shared__ float s_freq[64];  // RoPE frequencies of the n_rot/2 pairs
-  __shared__ float s_mx[2][2][kPfM];   // [tile parity][column half][row]: partial row maxima
+  __shared__ float s_ref[2][kPfM];     // [tile parity][row]: the reference maximum that tile left
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
@@ -122,10 +131,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     return;
   }
   const uint32_t sQ = base;
-  const uint32_t sK = sQ + kPfQBytes;                       // slot s at + s * 16 KB
-  const uint32_t sV = sK + kPfKSlots * kPfKChunkBytes;      // slot s at + s * 32 KB
+  const uint32_t sK = sQ + kPfQBytes;                       // slot s at + s * 32 KB
+  const uint32_t sV = sK + kPfKSlots * kPfKUnitBytes;       // slot s at + s * 32 KB
   uint8_t *gQ = smem_raw;                                   // generic pointer to sQ
-  uint8_t *gV = smem_raw + kPfQBytes + kPfKSlots * kPfKChunkBytes;
+  uint8_t *gV = smem_raw + kPfQBytes + kPfKSlots * kPfKUnitBytes;
   const uint32_t bars = smem_u32(s_bars);
 
   if (threadIdx.x == 0) {
@@ -139,10 +148,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarVFull + i), 1);
       mbar_init(bars + 8 * (kBarVFree + i), 1);
       mbar_init(bars + 8 * (kBarS + i), 1);
-      mbar_init(bars + 8 * (kBarP + i), 8);   // one elected lane per softmax warp
-      mbar_init(bars + 8 * (kBarX + i), 8);
+      mbar_init(bars + 8 * (kBarP + i), 4);   // one elected lane per softmax warp of the tile's set
       mbar_init(bars + 8 * (kBarO + i), 1);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(bars + 8 * (kBarR + i), 1);
     mbar_init(bars + 8 * kBarQ, 8);          // one per prologue warp
     fence_barrier_init();
   }
@@ -245,12 +254,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   float l_run = 0.f;                 // softmax threads: row sum
   float m_ref = -1.0e30f;            //                  reference maximum (log2 units)
 
+  if (warp >= 8) {
   if (warp == 8) {
     // =============================== K producer ====================================
-    // chunk g = 4 j + c: keys of tile j, dims [64 c, 64 c + 64), into slot g % 6
+    // unit g = 2 j + u: keys of tile j, dims [128 u, 128 u + 128) as two 64-dim chunks, into
+    // slot g % 3 -- one barrier per unit: the issuing thread pays for every wait and commit
     if (lane == 0) {
       int slot = 0, use = 0;
-      for (int g = 0; g < 4 * nt; ++g) {
+      for (int g = 0; g < 2 * nt; ++g) {
         if (use > 0 && !mbar_wait(bars + 8 * (kBarKFree + slot), (use - 1) & 1, p.status, 11)) {
           s_abort = 1;
           break;
@@ -260,8 +271,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         if (RD_PF_DEBUG(p) & 32) {
           mbar_arrive(full);
         } else {
-          mbar_expect_tx(full, kPfKChunkBytes);
-          tma_load_2d(sK + slot * kPfKChunkBytes, &p.tm_k, kvh * kHeadDim + 64 * (g & 3), (jt0 + (g >> 2)) * kPfN, full);
+          mbar_expect_tx(full, kPfKUnitBytes);
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(sK + slot * kPfKUnitBytes + h * kPfKChunkBytes, &p.tm_k,
+                        kvh * kHeadDim + 128 * (g & 1) + 64 * h, (jt0 + (g >> 1)) * kPfN, full);
         }
         if (++slot == kPfKSlots) {
           slot = 0;
@@ -307,34 +321,45 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       int slot = 0, use = 0;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
+        RD_PF_TRACE(2, j, 0);
         // score buffer st still holds P(j-2) until P V of tile j-2 has read it
         if (j >= 2 && !mbar_wait(bars + 8 * (kBarO + st), ((j - 2) >> 1) & 1, p.status, 15)) {
           ok = false;
           break;
         }
         const uint32_t d_s = tmem + kTmemS + 128 * st;
-        for (int c = 0; c < 4 && ok; ++c) {
+        RD_PF_TRACE(2, j, 1);
+        for (int u = 0; u < 2 && ok; ++u) {
           if (!mbar_wait(bars + 8 * (kBarKFull + slot), use & 1, p.status, 12)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          // A = Q sub-tile c ([128 rows][64 dims]), B = K chunk ([128 keys][64 dims]), both
-          // K-major with 8-row groups 1 KB apart; four steps of 16 dims = 32 bytes each
-          const uint64_t a0 = dq + (uint64_t)((c * (kPfM * 128)) >> 4);
-          const uint64_t b0 = dk + (uint64_t)((slot * kPfKChunkBytes) >> 4);
+          if (u == 0) RD_PF_TRACE(2, j, 3);
+          // per 64-dim chunk c = 2 u + h: A = Q sub-tile c ([128 rows][64 dims]), B = K chunk
+          // ([128 keys][64 dims]), both K-major with 8-row groups 1 KB apart; four steps of
+          // 16 dims = 32 bytes each
           if (!(RD_PF_DEBUG(p) & 8)) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              tc_mma_f16(d_s, a0 + (uint64_t)(2 * kk), b0 + (uint64_t)(2 * kk), idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+            for (int h = 0; h < 2; ++h) {
+              const uint64_t a0 = dq + (uint64_t)(((2 * u + h) * (kPfM * 128)) >> 4);
+              const uint64_t b0 = dk + (uint64_t)((slot * kPfKUnitBytes + h * kPfKChunkBytes) >> 4);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                tc_mma_f16(d_s, a0 + (uint64_t)(2 * kk), b0 + (uint64_t)(2 * kk), idesc_s,
+                           (u > 0 || h > 0 || kk > 0) ? 1u : 0u);
+            }
           }
-          tc_commit(bars + 8 * (kBarKFree + slot));  // the chunk can be refilled
+          if (u == 0) RD_PF_TRACE(2, j, 4);
+          tc_commit(bars + 8 * (kBarKFree + slot));  // the unit can be refilled
+          if (u == 0) RD_PF_TRACE(2, j, 5);
           if (++slot == kPfKSlots) {
             slot = 0;
             ++use;
           }
         }
         tc_commit(bars + 8 * (kBarS + st));
+        RD_PF_TRACE(2, j, 2);
       }
       if (!ok) s_abort = 1;
     }
@@ -346,10 +371,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
+        RD_PF_TRACE(3, j, 0);
         if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) {
           ok = false;
           break;
         }
+        RD_PF_TRACE(3, j, 1);
         for (int u = 0; u < 2 && ok; ++u) {
           const int g = 2 * j + u, slot = g & 1;
           if (!mbar_wait(bars + 8 * (kBarVFull + slot), (g >> 1) & 1, p.status, 19)) {
@@ -370,97 +397,127 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           tc_commit(bars + 8 * (kBarVFree + slot));  // the V unit can be refilled
         }
         tc_commit(bars + 8 * (kBarO + st));  // score buffer reusable, O settled
+        RD_PF_TRACE(3, j, 2);
       }
       if (!ok) s_abort = 1;
     }
+  }
   } else {
-    // ================== softmax: thread = (row r, 64-column half ch) ==================
-    const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7;
+    // ========= softmax: thread = (row r, tile parity): warps 0-3 take the even key =========
+    // tiles of this CTA, warps 4-7 the odd ones, a whole 128-key row of scores per thread.
+    // The two sets run one tile apart, so the tensor-memory loads, the maxima and the waits
+    // of tile j + 1 overlap the exponentials of tile j. What the tiles of a row share is the
+    // reference maximum of the one accumulator: it is handed from tile to tile through
+    // s_ref and one mbarrier per (warp pair, parity) -- after a tile's maxima are known,
+    // before its exponentials.
+    const int r = threadIdx.x & (kPfM - 1), set = threadIdx.x >> 7;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t bar_ref = bars + 8 * (kBarR + 2 * (warp & 3));
     bool ok = true;
-    for (int j = 0; j < nt && ok; ++j) {
-      const int st = j & 1;
+    for (int j = set; j < nt && ok; j += 2) {
+      const int st = set;   // tile j's score buffer: j & 1
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 0);
+      // the reference tile j - 1 left: its set published it right after its own maxima,
+      // long before this tile's scores are ready -- fetched first, off the critical path
+      float m_prev = -1.0e30f;
+      if (j > 0) {
+        if (!mbar_wait(bar_ref + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, p.status, 20)) { ok = false; break; }
+        m_prev = s_ref[(j - 1) & 1][r];
+      }
       if (!mbar_wait(bars + 8 * (kBarS + st), (j >> 1) & 1, p.status, 14)) { ok = false; break; }
       tc_fence_after();
-      uint32_t s0[32], s1[32];
-      const uint32_t scol = lane_addr + kTmemS + 128 * st + 64 * ch;
-      tmem_ld32(scol, s0);
-      tmem_ld32(scol + 32, s1);
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 1);
+      uint32_t sc[4][32];
+      const uint32_t scol = lane_addr + kTmemS + 128 * st;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(scol + 32 * c, sc[c]);
       tmem_wait_ld();
-      const int key0 = (jt0 + j) * kPfN + 64 * ch;
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 2);
+      const int key0 = (jt0 + j) * kPfN;
       // only tiles that reach past some row's last key need the causal mask
-      if (__any_sync(0xffffffffu, key0 + 63 > my_pos)) {
+      if (__any_sync(0xffffffffu, key0 + kPfN - 1 > my_pos)) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (key0 + i > my_pos) s0[i] = 0xff800000u;  // -inf
-          if (key0 + 32 + i > my_pos) s1[i] = 0xff800000u;
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + 32 * c + i > my_pos) sc[c][i] = 0xff800000u;  // -inf
       }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // eight independent chains of three-input maxima
+      float mx[8];
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        mx[i & 3] = fmaxf(mx[i & 3], fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
-      float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      s_mx[st][ch][r] = mt;
-      // exchange through an mbarrier (bounded wait) rather than bar.sync: a thread that
-      // gave up on a wait must not leave the others parked on a hardware barrier. (The
-      // exchange also orders both halves' score loads before either half overwrites the
-      // buffer with P.)
+      for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
+      const float mt = fmaxf(max3(mx[0], mx[1], mx[2]), fmaxf(max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      const bool grow = __any_sync(0xffffffffu, mt > m_prev + kLazyThreshold);
+      const float m_new = grow ? fmaxf(m_prev, mt) : m_prev;
+      s_ref[j & 1][r] = m_new;
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + 8 * (kBarX + st));
-      if (!mbar_wait(bars + 8 * (kBarX + st), (j >> 1) & 1, p.status, 20)) { ok = false; break; }
-      mt = fmaxf(mt, s_mx[st][ch ^ 1][r]);   // both halves now agree on the row maximum
-      const bool grow = mt > m_ref + kLazyThreshold;
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = fmaxf(m_ref, mt);
-        const float f = ex2(m_ref - m_new);   // 1 for rows that keep their reference
-        m_ref = m_new;
-        l_run *= f;
-        if (j > 0) {  // O holds data only after the first P V; and P V of tile j-1 must be done
-          if (!mbar_wait(bars + 8 * (kBarO + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-#pragma unroll 1
-          for (int c = 0; c < kHeadDim / 64; ++c) {   // this half's 128 output columns
-            uint32_t o[32];
-            const uint32_t col = kTmemO + 128 * ch + 32 * c;
-            tmem_ld32(lane_addr + col, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st32(lane_addr + col, o);
-          }
-          tmem_wait_st();
+      if (lane == 0) mbar_arrive(bar_ref + 8 * (j & 1));
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 3);
+      l_run *= ex2(m_ref - m_new);   // this set's sum moves to the new reference (m_ref: its last one)
+      m_ref = m_new;
+      if (grow && j > 0) {
+        // O is rescaled in tensor memory: P V of tile j - 1 must be done, and no later one
+        // can start before this tile's P arrives
+        const float f = ex2(m_prev - m_new);   // 1 for rows that keep their reference
+        if (!mbar_wait(bars + 8 * (kBarO + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status, 17)) {
+          ok = false;
+          break;
         }
-      }
-      // P = 2^(s - m_ref) as f16 pairs, written over the score buffer: keys 64ch..64ch+63
-      // of row r become columns 32ch..32ch+31 (the A operand of P V, read from TMEM)
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pw[16];
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < kHeadDim / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(lane_addr + kTmemO + 32 * c, o);
+          tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s0[2 * i]) : ex2(__uint_as_float(s0[2 * i]) - m_ref);
-        const float p1 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s0[2 * i + 1]) : ex2(__uint_as_float(s0[2 * i + 1]) - m_ref);
-        ls[i & 3] += p0 + p1;
-        pw[i] = pack_h2(p0, p1);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st32(lane_addr + kTmemO + 32 * c, o);
+        }
+        tmem_wait_st();
       }
-      const uint32_t pcol = lane_addr + kTmemS + 128 * st + 32 * ch;
-      tmem_st16(pcol, pw);
+      // P = 2^(s - m_ref) as f16 pairs, written over the score buffer: key k of row r
+      // becomes half k & 1 of column k / 2 (the A operand of P V, read from TMEM); the
+      // columns a chunk overwrites hold scores that are already in registers
+      // (s - m) and the row sum go through the packed f32x2 adds, two scores per
+      // instruction: measured alone, one warp then needs ~1200 cycles per 128-score row
+      // (the 128 exponentials alone are 1024 on the special-function unit) against ~1600
+      // with scalar adds
+      const unsigned long long neg_m = f2_pack(-m_new, -m_new);
+      unsigned long long ls2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s1[2 * i]) : ex2(__uint_as_float(s1[2 * i]) - m_ref);
-        const float p1 = (RD_PF_DEBUG(p) & 1) ? __uint_as_float(s1[2 * i + 1]) : ex2(__uint_as_float(s1[2 * i + 1]) - m_ref);
-        ls[i & 3] += p0 + p1;
-        pw[i] = pack_h2(p0, p1);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1;
+          f2_unpack(f2_add(f2_pack(__uint_as_float(sc[c][2 * i]), __uint_as_float(sc[c][2 * i + 1])), neg_m), x0, x1);
+          if (!(RD_PF_DEBUG(p) & 1)) {
+            x0 = ex2(x0);
+            x1 = ex2(x1);
+          }
+          ls2[i & 3] = f2_add(ls2[i & 3], f2_pack(x0, x1));
+          pw[i] = (RD_PF_DEBUG(p) & 2) ? __float_as_uint(x0) : pack_h2(x0, x1);
+        }
+        if (!(RD_PF_DEBUG(p) & 16)) tmem_st16(scol + 16 * c, pw);
+        else if (pw[0] == 0x12345678u && pw[7] == 0x9abcdefu) l_run += 1.f;   // keeps the values live
       }
-      tmem_st16(pcol + 16, pw);
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      {
+        float a0, a1, a2, a3;
+        f2_unpack(f2_add(ls2[0], ls2[1]), a0, a1);
+        f2_unpack(f2_add(ls2[2], ls2[3]), a2, a3);
+        l_run += (a0 + a1) + (a2 + a3);
+      }
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 4);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarP + st));
+      if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 5);
     }
     if (ok && nt > 0 && !mbar_wait(bars + 8 * (kBarO + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
       ok = false;
@@ -470,8 +527,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
 
   __syncthreads();
   const bool aborted = s_abort != 0;
-  // the two column halves of a row add their partial sums (s_mx is free now)
-  if (warp < 8) s_mx[0][threadIdx.x >> 7][threadIdx.x & (kPfM - 1)] = l_run;
+  // the two sets' row sums, each with the reference it is expressed in: [set][sum,
+  // reference][row], over the K ring (every load into it has been consumed by now)
+  float (*s_fin)[2][kPfM] = reinterpret_cast<float (*)[2][kPfM]>(smem_raw + kPfQBytes);
+  if (warp < 8) {
+    s_fin[threadIdx.x >> 7][0][threadIdx.x & (kPfM - 1)] = l_run;
+    s_fin[threadIdx.x >> 7][1][threadIdx.x & (kPfM - 1)] = m_ref;
+  }
   __syncthreads();
 
   // ---- epilogue: O / l (x sigmoid(gate)) -> global, 64 columns at a time ----
@@ -483,7 +545,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     // staging tile and named barrier
     const int r = threadIdx.x & (kPfM - 1), ch = threadIdx.x >> 7, gt = threadIdx.x & (kPfM - 1);
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const float l_tot = s_mx[0][0][r] + s_mx[0][1][r];
+    // both sums at the reference the last tile left (a set without tiles: sum 0)
+    const float m_fin = nt > 0 ? s_ref[(nt - 1) & 1][r] : -1.0e30f;
+    const float l_tot = s_fin[0][0][r] * ex2(s_fin[0][1][r] - m_fin) + s_fin[1][0][r] * ex2(s_fin[1][1][r] - m_fin);
     const bool rec_mode = gridDim.z > 1;   // un-normalised records for prefill_merge_kernel
     const float inv = (l_tot > 0.f && !aborted) ? (rec_mode ? 1.0f : 1.0f / l_tot) : 0.f;
     const bool have = nt > 0 && !aborted;
@@ -491,7 +555,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       // header of this row's record; natural-log units like every record of the library
       float *rec = p.records + (((size_t)(row0 + r) * p.n_head + head) * gridDim.z + blockIdx.z) * kRec;
       const bool some = have && l_tot > 0.f;
-      rec[0] = some ? m_ref * 0.6931471805599453f : -INFINITY;
+      rec[0] = some ? m_fin * 0.6931471805599453f : -INFINITY;
       rec[1] = some ? l_tot : 0.f;
     }
     const uint32_t stg = sQ + ch * (kPfM * 256);
@@ -696,3 +760,9 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
 }
 
 }  // namespace rd
+
+#ifdef RD_TIMING_SWITCHES
+extern "C" int rd_debug_pf_trace(unsigned long long *host_dst) {
+  return cudaMemcpyFromSymbol(host_dst, g_pf_trace, sizeof(g_pf_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -33,11 +33,6 @@ __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
   asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
   return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
 // PUSH of one (head row, dim quarter) by NG groups of 64 threads (thread = (group ty, dim
 // tx)): group ty walks records ty, ty + NG, ... with four loads in flight and a local
