@@ -49,15 +49,19 @@
 // in builds with -DRD_TIMING_SWITCHES; a default build compiles them out.
 #ifdef RD_TIMING_SWITCHES
 #define RD_PF_DEBUG(p) ((p).debug)
-// phase trace of CTA (0, 0, 0): [role 0..3][tile 0..47][point 0..7] clock64 values
-__device__ unsigned long long g_pf_trace[4][48][8];
-#define RD_PF_TRACE(role, j, pt)                                                              \
-  do {                                                                                        \
-    if ((p.debug & 64) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 48)  \
-      g_pf_trace[role][j][pt] = clock64();                                                    \
-  } while (0)
 #else
 #define RD_PF_DEBUG(p) 0
+#endif
+// -DRD_PF_TRACING (timing builds only): phase trace of CTA (0, 0, 0),
+// [role 0..3][tile 0..47][point 0..7] clock64 values, read back with rd_debug_pf_trace
+#ifdef RD_PF_TRACING
+__device__ unsigned long long g_pf_trace[4][48][8];
+#define RD_PF_TRACE(role, j, pt)                                                  \
+  do {                                                                            \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 48)        \
+      g_pf_trace[role][j][pt] = clock64();                                        \
+  } while (0)
+#else
 #define RD_PF_TRACE(role, j, pt) do { } while (0)
 #endif
 
@@ -105,8 +109,9 @@ struct PrefillArgs {
 };
 
 // Barrier slots (8 bytes each).
-enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarO = 20,
-       kBarQ = 22, kBarR = 23, kBarCount = 31 };   // kBarR: [warp pair 0..3][tile parity]
+enum { kBarKFull = 0, kBarKFree = 6, kBarVFull = 12, kBarVFree = 14, kBarS = 16, kBarP = 18, kBarO = 22,
+       kBarQ = 24, kBarR = 25, kBarCount = 33 };   // kBarP: [score buffer][64-key half of P];
+                                                   // kBarR: [warp pair 0..3][tile parity]
 
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_constant__ PrefillArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -148,7 +153,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarVFull + i), 1);
       mbar_init(bars + 8 * (kBarVFree + i), 1);
       mbar_init(bars + 8 * (kBarS + i), 1);
-      mbar_init(bars + 8 * (kBarP + i), 4);   // one elected lane per softmax warp of the tile's set
+      mbar_init(bars + 8 * (kBarP + 2 * i), 4);       // one elected lane per softmax warp of the
+      mbar_init(bars + 8 * (kBarP + 2 * i + 1), 4);   // tile's set, per 64-key half of P
       mbar_init(bars + 8 * (kBarO + i), 1);
     }
     for (int i = 0; i < 8; ++i) mbar_init(bars + 8 * (kBarR + i), 1);
@@ -372,12 +378,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j & 1;
         RD_PF_TRACE(3, j, 0);
-        if (!mbar_wait(bars + 8 * (kBarP + st), (j >> 1) & 1, p.status, 13)) {
-          ok = false;
-          break;
-        }
-        RD_PF_TRACE(3, j, 1);
         for (int u = 0; u < 2 && ok; ++u) {
+          // P arrives in two halves of 64 keys: P V of the first runs while the softmax
+          // threads are still on the second
+          if (!mbar_wait(bars + 8 * (kBarP + 2 * st + u), (j >> 1) & 1, p.status, 13)) {
+            ok = false;
+            break;
+          }
+          if (u == 0) RD_PF_TRACE(3, j, 1);
           const int g = 2 * j + u, slot = g & 1;
           if (!mbar_wait(bars + 8 * (kBarVFull + slot), (g >> 1) & 1, p.status, 19)) {
             ok = false;
@@ -505,6 +513,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
         if (!(RD_PF_DEBUG(p) & 16)) tmem_st16(scol + 16 * c, pw);
         else if (pw[0] == 0x12345678u && pw[7] == 0x9abcdefu) l_run += 1.f;   // keeps the values live
+        if (c == 1) {   // the first 64 keys of P are complete: hand them to the P V issuer
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + 8 * (kBarP + 2 * st));
+        }
       }
       {
         float a0, a1, a2, a3;
@@ -516,7 +530,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + 8 * (kBarP + st));
+      if (lane == 0) mbar_arrive(bars + 8 * (kBarP + 2 * st + 1));
       if ((threadIdx.x & 127) == 0) RD_PF_TRACE(set, j, 5);
     }
     if (ok && nt > 0 && !mbar_wait(bars + 8 * (kBarO + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, p.status, 16))
@@ -761,7 +775,7 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
 
 }  // namespace rd
 
-#ifdef RD_TIMING_SWITCHES
+#ifdef RD_PF_TRACING
 extern "C" int rd_debug_pf_trace(unsigned long long *host_dst) {
   return cudaMemcpyFromSymbol(host_dst, g_pf_trace, sizeof(g_pf_trace)) == cudaSuccess ? 0 : -1;
 }
