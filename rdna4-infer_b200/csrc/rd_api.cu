@@ -815,17 +815,20 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   if ((rc = current_device(&dev)) != RD_OK) return rc;
   DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
   if (status == nullptr) return RD_ERR_CUDA;
+  // scratch: [rotated f16 queries, if the call rotates][key-split records, if any]
   int splits = prefill_splits(n_q, keys_total, n_head, sm_count(dev));
+  const size_t rope_need = n_rot > 0 ? align256(prefill_rope_bytes(n_q, n_head)) : 0;
   const size_t need = prefill_record_bytes(n_q, n_head, splits);
-  if (splits > 1) {
-    if (records == nullptr) {
-      records = ensure_workspace(dev, need);
-      record_bytes = records != nullptr ? need : 0;
-    }
-    if (record_bytes < need) splits = 1;   // no room: one CTA per (token tile, head) walks all keys
+  if (records == nullptr && rope_need + (splits > 1 ? need : 0) > 0) {
+    records = ensure_workspace(dev, rope_need + need);
+    record_bytes = records != nullptr ? rope_need + need : 0;
   }
+  if (record_bytes < rope_need) return records == nullptr ? RD_ERR_CUDA : RD_ERR_WORKSPACE;
+  void *rope_cs = rope_need > 0 ? records : nullptr;
+  float *recs = (float *)((unsigned char *)records + rope_need);
+  if (splits > 1 && record_bytes - rope_need < need) splits = 1;   // no room: one CTA per (token tile, head) walks all keys
   return launch_prefill(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, scale, n_rot,
-                        freq_base, status, (float *)records, splits, (cudaStream_t)stream);
+                        freq_base, status, recs, splits, rope_cs, (cudaStream_t)stream);
 }
 
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
@@ -854,7 +857,7 @@ size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int n_q, int keys
   if (!known_type(k_type) || !known_type(v_type) || n_q < 1 || keys_total <= 0 || n_head < 1 ||
       n_head_kv < 1 || head_dim != kHeadDim || current_device(&dev) != RD_OK)
     return 0;
-  return prefill_copy_bytes(k_type, v_type, keys_total, n_head_kv) +
+  return prefill_copy_bytes(k_type, v_type, keys_total, n_head_kv) + align256(prefill_rope_bytes(n_q, n_head)) +
          align256(prefill_record_bytes(n_q, n_head, prefill_splits(n_q, keys_total, n_head, sm_count(dev))));
 }
 

@@ -96,9 +96,8 @@ struct PrefillArgs {
   int n_head;
   int nkv;
   float qscale;          // scale * log2(e)
-  int n_rot;             // 0: the queries are already rotated
-  float freq_base;
-  RopeTable rope;        // host-computed frequencies of the n_rot/2 <= 32 pairs
+  alignas(64) CUtensorMap tm_q;  // q16 != 0: the rotated, scaled f16 queries q_prep_kernel wrote
+  int q16;               // 1: Q tile by TMA from tm_q; 0: converted from `q` (f32, no rotation) here
   int debug;             // timing experiments only (bit mask), 0 in production
   DeviceStatus *status;
   // Split over the keys (gridDim.z > 1): CTA (tile, head, z) walks only its share of the
@@ -119,10 +118,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_maxpos;
   __shared__ int s_abort;
-  __shared__ float s_freq[64];  // RoPE frequencies of the n_rot/2 pairs
   __shared__ float s_ref[2][kPfM];     // [tile parity][row]: the reference maximum that tile left
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 0);   // kernel entry
   const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
   const int head = blockIdx.y;
   const int kvh = head / kGroup;
@@ -139,7 +138,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   const uint32_t sK = sQ + kPfQBytes;                       // slot s at + s * 32 KB
   const uint32_t sV = sK + kPfKSlots * kPfKUnitBytes;       // slot s at + s * 32 KB
   uint8_t *gQ = smem_raw;                                   // generic pointer to sQ
-  uint8_t *gV = smem_raw + kPfQBytes + kPfKSlots * kPfKUnitBytes;
   const uint32_t bars = smem_u32(s_bars);
 
   if (threadIdx.x == 0) {
@@ -158,11 +156,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       mbar_init(bars + 8 * (kBarO + i), 1);
     }
     for (int i = 0; i < 8; ++i) mbar_init(bars + 8 * (kBarR + i), 1);
-    mbar_init(bars + 8 * kBarQ, 8);          // one per prologue warp
+    mbar_init(bars + 8 * kBarQ, p.q16 ? 1 : 8);   // the TMA issuer, or one per converting warp
     fence_barrier_init();
   }
-  if (p.n_rot > 0 && (int)threadIdx.x >= 64 && (int)threadIdx.x < 64 + p.n_rot / 2)
-    s_freq[threadIdx.x - 64] = p.rope.f[threadIdx.x - 64];
   if (warp == 9) {  // TMEM: 512 columns for this CTA (one CTA per SM: no contention)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -171,6 +167,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   __syncthreads();
+  if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 1);   // barriers + TMEM allocated
 
   // ---- positions of this tile's rows; the last key any of them attends ----
   int my_pos = -1;
@@ -186,6 +183,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 2);   // positions known
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
   const int maxpos = s_maxpos;
@@ -193,68 +191,48 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   const int jt0 = (int)(((int64_t)nt_all * blockIdx.z) / gridDim.z);        // this CTA's share of them
   const int nt = (int)(((int64_t)nt_all * (blockIdx.z + 1)) / gridDim.z) - jt0;
 
-  // ---- prologue: Q rows -> f16 in the swizzled K-major layout (warps 0-7, 16 rows each) ----
-  if (warp < 8) {
-    // cos/sin of every (row, pair) of this warp's 16 rows -- lane = (row, half of the
-    // pairs) -- parked in the V ring (the V producer starts only after this prologue):
-    // 4 KB per warp
-    float2 *cs_tab = reinterpret_cast<float2 *>(gV) + warp * (16 * 32);
-    const int pairs = p.n_rot / 2;
-    if (pairs > 0) {
-      const int gr_l = row0 + warp * 16 + (lane & 15);
-      const float fpos = gr_l < p.n_q ? (float)p.pos[gr_l] : 0.f;
-      for (int i = (lane >> 4); i < pairs; i += 2) {
-        float c, s;
-        sincosf(fpos * s_freq[i], &s, &c);
-        cs_tab[(lane & 15) * 32 + i] = make_float2(c, s);
-      }
-      __syncwarp();
-    }
-#pragma unroll 8
-    for (int rr = 0; rr < 16; ++rr) {
-      const int r = warp * 16 + rr;      // row inside the tile
-      const int gr = row0 + r;
-      float v[8], other[8];
-      // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims p and p + n_rot/2 sit in lanes
-      // l and l ^ (n_rot/16) at the same element index. Those lanes load their partner's
-      // eight values as well (same cache lines) instead of shuffling: a shuffle inside
-      // this loop keeps the compiler from batching the rows' global loads.
-      const int half_lanes = p.n_rot / 16;
-      const bool rot = pairs > 0 && lane < 2 * half_lanes;
+  // ---- prologue: the Q tile as f16 in the swizzled K-major layout ----
+  if (p.q16) {
+    // rotated, scaled and rounded by q_prep_kernel: four TMA boxes of [128 rows][64 dims]
+    // (rows past n_q are filled with zeros)
+    if (threadIdx.x == 0) {
+      pdl_wait();   // that pass has completed (this launch may have started under it)
+      const uint32_t full = bars + 8 * kBarQ;
+      mbar_expect_tx(full, kPfQBytes);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = other[i] = 0.f;
+      for (int c = 0; c < 4; ++c)
+        tma_load_2d(sQ + c * (kPfM * 128), &p.tm_q, head * kHeadDim + 64 * c, row0, full);
+    }
+  } else if (warp < 8) {
+    // f32 rows -> x scale * log2(e) -> f16, warps 0-7, 16 rows each. All 16 rows of the warp
+    // are requested before any is converted (32 float4 per lane): the conversion is bound
+    // by the latency of these loads, paid once this way.
+    float4 qa[16], qb[16];
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) {
+      const int gr = row0 + warp * 16 + rr;
+      qa[rr] = qb[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (gr < p.n_q) {
         const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim);
-        const float4 a = src[2 * lane], b = src[2 * lane + 1];
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        if (rot) {
-          const int pl = lane ^ half_lanes;
-          const float4 c = src[2 * pl], d = src[2 * pl + 1];
-          other[0] = c.x; other[1] = c.y; other[2] = c.z; other[3] = c.w;
-          other[4] = d.x; other[5] = d.y; other[6] = d.z; other[7] = d.w;
-        }
+        qa[rr] = src[2 * lane];
+        qb[rr] = src[2 * lane + 1];
       }
-      if (rot) {
-        const bool lo = lane < half_lanes;
+    }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float2 cs = cs_tab[rr * 32 + 8 * (lo ? lane : lane - half_lanes) + i];
-          v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other[i], cs.y))
-                    : __fadd_rn(__fmul_rn(other[i], cs.y), __fmul_rn(v[i], cs.x));
-        }
-      }
-      const uint32_t w0 = pack_h2(v[0] * p.qscale, v[1] * p.qscale);
-      const uint32_t w1 = pack_h2(v[2] * p.qscale, v[3] * p.qscale);
-      const uint32_t w2 = pack_h2(v[4] * p.qscale, v[5] * p.qscale);
-      const uint32_t w3 = pack_h2(v[6] * p.qscale, v[7] * p.qscale);
+    for (int rr = 0; rr < 16; ++rr) {
+      const int r = warp * 16 + rr;      // row inside the tile
+      const uint32_t w0 = pack_h2(qa[rr].x * p.qscale, qa[rr].y * p.qscale);
+      const uint32_t w1 = pack_h2(qa[rr].z * p.qscale, qa[rr].w * p.qscale);
+      const uint32_t w2 = pack_h2(qb[rr].x * p.qscale, qb[rr].y * p.qscale);
+      const uint32_t w3 = pack_h2(qb[rr].z * p.qscale, qb[rr].w * p.qscale);
       // lane = 16-byte chunk of the row: sub-tile lane/8, chunk lane%8, swizzled by the row
       const uint32_t dst = sQ + (lane >> 3) * (kPfM * 128) + r * 128 + (((lane & 7) ^ (r & 7)) << 4);
       sts128(dst, w0, w1, w2, w3);
     }
     fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
     __syncwarp();
-    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // S MMAs and V loads wait for all 8 warps
+    if (lane == 0) mbar_arrive(bars + 8 * kBarQ);  // the S MMAs wait for all 8 warps
+    if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 3);   // this warp's Q rows converted
   }
 
   float l_run = 0.f;                 // softmax threads: row sum
@@ -293,7 +271,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     // =============================== V producer ====================================
     // unit g = 2 j + u: keys [128 j + 64 u, + 64) of all 256 dims, into slot g % 2
     if (lane == 0) {
-      bool ok = mbar_wait(bars + 8 * kBarQ, 0, p.status, 21);  // the prologue parks a table here
+      bool ok = true;
       for (int g = 0; g < 2 * nt && ok; ++g) {
         const int slot = g & 1;
         if (g >= 2 && !mbar_wait(bars + 8 * (kBarVFree + slot), ((g >> 1) - 1) & 1, p.status, 22)) {
@@ -495,7 +473,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
       // instruction: measured alone, one warp then needs ~1200 cycles per 128-score row
       // (the 128 exponentials alone are 1024 on the special-function unit) against ~1600
       // with scalar adds
-      const unsigned long long neg_m = f2_pack(-m_new, -m_new);
+      unsigned long long neg_m = f2_pack(-m_new, -m_new);
       unsigned long long ls2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -518,6 +496,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + 8 * (kBarP + 2 * st));
+          // keeps the second half's arithmetic behind the hand-over (the compiler would
+          // otherwise hoist all 128 exponentials above the first store)
+          asm volatile("mov.b64 %0, %0;" : "+l"(neg_m)::"memory");
         }
       }
       {
@@ -549,6 +530,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     s_fin[threadIdx.x >> 7][1][threadIdx.x & (kPfM - 1)] = m_ref;
   }
   __syncthreads();
+  if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 4);   // main loop done, sums exchanged
 
   // ---- epilogue: O / l (x sigmoid(gate)) -> global, 64 columns at a time ----
   // staging tile [128 rows][64 floats] aliases the Q region; 16-byte chunk q of row r is
@@ -651,6 +633,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 5);   // epilogue stores done
   if (warp == 9) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");
@@ -698,6 +681,48 @@ prefill_merge_kernel(const float *__restrict__ records, float *__restrict__ out,
   *reinterpret_cast<float4 *>(out + (size_t)row * kHeadDim + 4 * tx) = o;
 }
 
+// Query pre-pass of the rotating prefill: one block per token. (cos, sin) of pos[t] * freq[i]
+// once per rotated pair (24 heads share them), then every head row: partial RoPE in f32 with
+// the operation order of the K side, x scale * log2(e), rounded to f16 -- [n_q][n_head][256]
+// f16, the layout the tile kernel's TMA boxes read. The tile kernel is launched directly
+// after it as a programmatic dependent launch.
+__global__ void __launch_bounds__(256)
+q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int n_head, int n_rot, float qscale,
+              uint4 *__restrict__ q16, const __grid_constant__ RopeTable tab) {
+  __shared__ float2 s_cs[32];
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pairs = n_rot / 2;
+  if ((int)threadIdx.x < pairs) {
+    float c, s;
+    sincosf((float)pos[t] * tab.f[threadIdx.x], &s, &c);
+    s_cs[threadIdx.x] = make_float2(c, s);
+  }
+  __syncthreads();
+  // lanes 0..(n_rot/8 - 1) hold the rotated dims; dims d and d + n_rot/2 sit in lanes l and
+  // l ^ (n_rot/16) at the same element index
+  const int half_lanes = n_rot / 16;
+  const bool rot = lane < 2 * half_lanes, lo = lane < half_lanes;
+  for (int head = warp; head < n_head; head += 8) {
+    const size_t row = (size_t)t * n_head + head;
+    const float4 *src = reinterpret_cast<const float4 *>(q + row * kHeadDim);
+    const float4 a = src[2 * lane], b = src[2 * lane + 1];
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
+      if (rot) {
+        const float2 cs = s_cs[8 * (lo ? lane : lane - half_lanes) + i];
+        v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
+                  : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
+      }
+    }
+    q16[row * 32 + lane] = make_uint4(pack_h2(v[0] * qscale, v[1] * qscale), pack_h2(v[2] * qscale, v[3] * qscale),
+                                      pack_h2(v[4] * qscale, v[5] * qscale), pack_h2(v[6] * qscale, v[7] * qscale));
+  }
+}
+size_t prefill_rope_bytes(int n_q, int n_head) { return (size_t)n_q * n_head * kHeadDim * 2; }
+
 // Key splits that fill the GPU, picked with a three-constant cost model measured on B200:
 // a key tile costs a CTA about 2 us, a CTA's prologue + epilogue about 9 us (the query
 // tile is converted and the result written whatever the key count), and the records cost
@@ -728,7 +753,7 @@ size_t prefill_record_bytes(int n_q, int n_head, int splits) {
 int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
                    const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
                    int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits,
-                   cudaStream_t st) {
+                   void *q16, cudaStream_t st) {
   PrefillArgs a;
   memset(&a, 0, sizeof(a));
   int rc = encode_f16_tmap(&a.tm_k, k, n_head_kv, keys_total, kPfN);
@@ -743,9 +768,11 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   a.n_head = n_head;
   a.nkv = n_head_kv;
   a.qscale = scale * 1.4426950408889634f;
-  a.n_rot = n_rot;
-  a.freq_base = freq_base;
-  a.rope = make_rope_table(n_rot, freq_base);
+  a.q16 = n_rot > 0 ? 1 : 0;
+  if (n_rot > 0) {
+    if (q16 == nullptr) return RD_ERR_WORKSPACE;
+    if ((rc = encode_f16_tmap(&a.tm_q, q16, n_head, n_q, kPfM)) != RD_OK) return rc;
+  }
   a.status = status;
   a.debug = 0;
 #ifdef RD_TIMING_SWITCHES
@@ -763,8 +790,27 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   if (n_splits < 1 || records == nullptr) n_splits = 1;
   a.records = records;
   const dim3 grid((unsigned)((n_q + kPfM - 1) / kPfM), (unsigned)n_head, (unsigned)n_splits);
-  prefill_kernel<<<grid, kPfThreads, kPfSmemBytes, st>>>(a);
-  if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+  if (n_rot > 0) {
+    q_prep_kernel<<<(unsigned)n_q, 256, 0, st>>>(q, pos, n_head, n_rot, a.qscale, (uint4 *)q16,
+                                                make_rope_table(n_rot, freq_base));
+    if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+    // the tile kernel may start while that pass runs; it waits for it (griddepcontrol)
+    // before it loads its Q tile
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kPfThreads);
+    cfg.dynamicSmemBytes = kPfSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, prefill_kernel, a) != cudaSuccess) return RD_ERR_CUDA;
+  } else {
+    prefill_kernel<<<grid, kPfThreads, kPfSmemBytes, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+  }
   if (n_splits > 1) {
     const int64_t n_rows = (int64_t)n_q * n_head;
     prefill_merge_kernel<<<(unsigned)((n_rows + 3) / 4), 256, 0, st>>>(records, out, gate, n_rows, n_splits);
