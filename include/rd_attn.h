@@ -23,7 +23,14 @@
  *     (rd_attn_decode, rd_attn_decode_split, rd_attn_batch, rd_attn_split_batch) grow
  *     a per-device workspace with cudaMalloc the first time a shape needs it, because
  *     148 SMs want more partial records than the reference's 16-split buffer holds.
- *     The *_ws entry points take the workspace from the caller and never allocate.
+ *     That workspace is ONE per device, shared by all streams and host threads: use
+ *     these launchers (and rd_fa2_prefill / rd_attn_prefill_fused, which grow it the
+ *     same way) from one stream per device, or order the streams yourself -- two calls
+ *     whose kernels overlap race on the records. A later, larger shape frees and
+ *     reallocates it, which leaves a CUDA graph captured earlier with the old pointer:
+ *     warm up with the largest shape before capturing, or use the *_ws entry points,
+ *     which take the workspace from the caller, never allocate and have no such
+ *     sharing (multi-stream and graph users).
  *
  * Every function returns RD_OK (0) or a negative RD_ERR_* code; nothing aborts and
  * nothing traps on the device. Shapes outside the supported set are refused with
@@ -342,10 +349,13 @@ int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const
 /* The same kernel with its fused edges (no single counterpart in the reference: it is
  * rope_launch on q, include/rdna4/attn.cuh:56-63, + the prefill attention + the sigmoid
  * gate of nn.cuh:405-420 in one launch). n_rot > 0 (a multiple of 16, <= 64) rotates
- * the first n_rot dims of every query row by its pos[] on load -- q itself is not
- * modified unless it aliases o; the K rows in the cache must already be rotated (use
- * rd_kv_append with pos). gate != NULL multiplies the output by sigmoid(gate); the gate
- * buffer is read only. q, o and gate must be 16-byte aligned. */
+ * the first n_rot dims of every query row by its pos[] -- in a pre-pass that writes the
+ * rotated, scaled queries as f16 into the library's grown workspace (512 bytes per token
+ * and head; the tile kernel starts under it as a programmatic dependent launch and loads
+ * its query tile by TMA), so q itself is not modified unless it aliases o; the K rows in
+ * the cache must already be rotated (use rd_kv_append with pos). gate != NULL multiplies
+ * the output by sigmoid(gate); the gate buffer is read only. q, o and gate must be 16-byte
+ * aligned. */
 int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o, const float *gate,
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
                           int head_dim, float scale, int n_rot, float freq_base, void *stream);
@@ -354,8 +364,8 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
  * serves with its chunk path, attn_split_batch_launch (include/rdna4/attn.cuh:958-1049, all
  * 6 x 6 K x V types; dispatch src/graph.cuh:1486-1527), where every one of the n_q tokens
  * re-streams and re-expands its prefix. Here the caches that are not f16 are expanded ONCE
- * into `workspace` (rd_attn_prefill_workspace_bytes, which also covers the records of the
- * key split below) with the exact values of the reference's dequantizing loads
+ * into `workspace` (rd_attn_prefill_workspace_bytes, which also covers the rotated f16
+ * queries of a call with n_rot > 0 and the records of the key split) with the exact values of the reference's dequantizing loads
  * (kv.h:174-368) rounded to f16, and the tcgen05 prefill kernel runs over that copy. Arguments as rd_attn_prefill_fused; token i attends
  * keys 0..pos[i], keys_total rows must exist. No allocation, no host synchronisation. */
 size_t rd_attn_prefill_workspace_bytes(int k_type, int v_type, int n_q, int keys_total, int n_head,

@@ -501,9 +501,11 @@ int rd_attn_decode_append_ws(const float *q, const float *k_new, const float *v_
 int rd_attn_decode_noalloc(const float *q, const void *k, const void *v, float *out, int t,
                            int n_head, int n_head_kv, int head_dim, float scale, int k_type,
                            int v_type, float *gate, void *stream) {
+  // the fixed array's own limit first: a size beyond it is refused as such, whatever
+  // else the shape check would say about it
+  if (n_head > RD_NOALLOC_MAX_HEADS) return RD_ERR_LIMIT;
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
   if (rc != RD_OK) return rc;
-  if (n_head > RD_NOALLOC_MAX_HEADS) return RD_ERR_LIMIT;
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return RD_ERR_NULL;
   if (!aligned(q, 4) || !aligned(out, 4) || !aligned(gate, 4)) return RD_ERR_ALIGN;
   if (!aligned(k, 16) || !aligned(v, 16)) return RD_ERR_ALIGN;

@@ -52,9 +52,26 @@ def test_noalloc_matches_allocating_entry_on_two_calls_in_a_row(cuda, rd, oracle
 def test_noalloc_rejects_sizes_beyond_its_fixed_maximum(rd):
     buf = np.zeros(64, dtype=np.float32)
     p = buf.ctypes.data   # never dereferenced: the limit check comes first
-    # 30 query heads (5 KV heads would be refused as a shape; 24 is the stated maximum)
+    # 48 query heads: beyond the stated maximum of 24, refused as a limit before anything else
     assert rd.lib.rd_attn_decode_noalloc(p, p, p, p, 3, 48, 8, 256, 0.0625, rd.F16, rd.F16, None,
-                                         None) in (rd.ERR_LIMIT, rd.ERR_UNSUPPORTED)
+                                         None) == rd.ERR_LIMIT
+    assert rd.lib.rd_attn_decode_noalloc(p, p, p, p, 3, 25, 4, 256, 0.0625, rd.F16, rd.F16, None,
+                                         None) == rd.ERR_LIMIT
     assert rd.lib.rd_attn_decode_noalloc(p, p, p, None, 3, 24, 4, 256, 0.0625, rd.F16, rd.F16, None,
                                          None) == rd.ERR_NULL
     assert "maximum" in rd.strerror(rd.ERR_LIMIT)
+
+
+
+def test_noalloc_split_cap_keeps_the_records_inside_the_fixed_array(rd):
+    """The entry plans with at most RD_NOALLOC_MAX_SPLITS (160) "SMs": on any part, heads x
+    splits x 258 floats stays inside the 24 x 160 x 258 array. rd_attn_plan is that planner
+    (host arithmetic when the SM count is given)."""
+    import ctypes as C
+    cap, heads = 160, 24
+    for sms in (148, 160, 161, 192, 1024):
+        for n_keys in (1, 500, 131001, 10 ** 7):
+            n = C.c_int(0)
+            assert rd.lib.rd_attn_plan(n_keys, 1, 4, rd.Q4_0, rd.Q4_0, min(sms, cap), None, None, C.byref(n)) == rd.OK
+            assert 1 <= n.value <= cap
+            assert heads * n.value * 258 <= heads * cap * 258
