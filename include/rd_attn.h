@@ -231,6 +231,27 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
                          int head_dim, float scale, int k_type, int v_type, void *workspace,
                          size_t workspace_bytes, void *stream);
 
+/* The same call in its two halves, for hosts that capture the decode step into a CUDA graph.
+ *   rd_attn_multi_plan    host arithmetic only: checks the descriptors, cuts the key ranges
+ *                         into work items and encodes the tensor maps into `plan`, host
+ *                         memory of rd_attn_multi_plan_bytes(n_seq, q_len) bytes, 16-byte
+ *                         aligned. pad_items > 0 pads the work list to exactly that many
+ *                         items (the extra CTAs leave at once), so that the grid of a
+ *                         captured launch stays valid while the contexts grow; a plan that
+ *                         needs more items returns RD_ERR_LIMIT (capture again with more).
+ *   rd_attn_multi_launch  one host-to-device copy of the plan into the workspace, the
+ *                         decode launch and the merge, on `stream`. With the plan in PINNED
+ *                         host memory the call can be captured, and a replay reads the plan
+ *                         as it is then: rewrite it with rd_attn_multi_plan (same n_seq,
+ *                         q_len, types and pad_items) between replays, after the previous
+ *                         replay's copy has completed. From pageable memory it behaves as
+ *                         rd_attn_decode_multi (which is these two calls in a row). */
+size_t rd_attn_multi_plan_bytes(int n_seq, int q_len);
+int rd_attn_multi_plan(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
+                       int head_dim, int k_type, int v_type, int pad_items, void *plan, size_t plan_bytes);
+int rd_attn_multi_launch(const void *plan, float scale, void *workspace, size_t workspace_bytes,
+                         void *stream);
+
 /* ---- context-sharded decode over several GPUs, exchange fused into the merge.
  * (No counterpart in the reference, which is single-GPU.)
  *

@@ -54,6 +54,9 @@ SIGNATURES = {
                                       _P]),
     "rd_attn_multi_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I]),
     "rd_attn_decode_multi": (_I, [_P, _I, _I, _I, _I, _I, _F, _I, _I, _P, C.c_size_t, _P]),
+    "rd_attn_multi_plan_bytes": (C.c_size_t, [_I, _I]),
+    "rd_attn_multi_plan": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _P, C.c_size_t]),
+    "rd_attn_multi_launch": (_I, [_P, _F, _P, C.c_size_t, _P]),
     "rd_shard_xbuf_bytes": (C.c_size_t, [_I, _I, _I]),
     "rd_attn_decode_sharded": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, C.c_size_t,
                                     _P, _P]),

@@ -539,16 +539,33 @@ size_t rd_attn_multi_workspace_bytes(int n_seq, int q_len, int n_head, int head_
          align256(items * (size_t)n_head * kRec * sizeof(float));
 }
 
-int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
-                         int head_dim, float scale, int k_type, int v_type, void *workspace,
-                         size_t workspace_bytes, void *stream) {
+// Plan of one multi-sequence call, in HOST memory: a header, then exactly the bytes the
+// launch copies to the start of the workspace (sequence descriptors with their tensor
+// maps, then the work list).
+struct MultiPlanHeader {
+  uint32_t magic;
+  int32_t n_seq, q_len, n_head, n_head_kv, k_type, v_type;
+  int32_t n_items, max_items;
+  uint64_t off_items, copy_bytes;
+};
+constexpr uint32_t kMultiPlanMagic = 0x52444d50u;   // "RDMP"
+constexpr size_t kMultiPlanHeaderBytes = 256;
+static_assert(sizeof(MultiPlanHeader) <= kMultiPlanHeaderBytes, "plan header");
+
+size_t rd_attn_multi_plan_bytes(int n_seq, int q_len) {
+  int dev;
+  if (n_seq < 1 || q_len < 1 || current_device(&dev) != RD_OK) return 0;
+  const size_t items = (size_t)multi_max_items(sm_count(dev), n_seq, q_len);
+  return kMultiPlanHeaderBytes + align256((size_t)n_seq * sizeof(DecodeSeq)) + align256(items * sizeof(int4));
+}
+
+int rd_attn_multi_plan(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
+                       int head_dim, int k_type, int v_type, int pad_items, void *plan, size_t plan_bytes) {
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
   if (rc != RD_OK) return rc;
-  if (n_seq < 0 || q_len < 1) return RD_ERR_SHAPE;
-  if (n_seq == 0) return RD_OK;
-  if (seqs == nullptr) return RD_ERR_NULL;
-  if (workspace == nullptr) return RD_ERR_WORKSPACE;
-  if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
+  if (n_seq < 1 || q_len < 1 || pad_items < 0) return RD_ERR_SHAPE;
+  if (seqs == nullptr || plan == nullptr) return RD_ERR_NULL;
+  if (!aligned(plan, 16)) return RD_ERR_ALIGN;
   for (int i = 0; i < n_seq; ++i) {
     const rd_attn_seq &s = seqs[i];
     if (s.q == nullptr || s.k == nullptr || s.v == nullptr || s.out == nullptr) return RD_ERR_NULL;
@@ -558,14 +575,12 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
   }
   int dev;
   if ((rc = current_device(&dev)) != RD_OK) return rc;
-  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
-  if (status == nullptr) return RD_ERR_CUDA;
   const int sms = sm_count(dev);
   const int max_items = multi_max_items(sms, n_seq, q_len);
   const size_t off_items = align256((size_t)n_seq * sizeof(DecodeSeq));
-  const size_t off_rec = off_items + align256((size_t)max_items * sizeof(int4));
-  const size_t need = off_rec + align256((size_t)max_items * n_head * kRec * sizeof(float));
-  if (workspace_bytes < need) return RD_ERR_WORKSPACE;
+  if (plan_bytes < kMultiPlanHeaderBytes + off_items + align256((size_t)max_items * sizeof(int4)))
+    return RD_ERR_WORKSPACE;
+  if (pad_items > max_items) return RD_ERR_LIMIT;
 
   // Key split: chunks of equal length over all sequences, about four CTAs per SM in
   // total, so that a 32k-key sequence and a 1k-key one load the SMs evenly.
@@ -578,9 +593,9 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
   }
   int64_t chunk = (total + 4 * sms - 1) / (4 * sms);
   if (chunk < 4) chunk = 4;
-  std::vector<unsigned char> host(off_rec);
-  DecodeSeq *hs = reinterpret_cast<DecodeSeq *>(host.data());
-  int4 *hi = reinterpret_cast<int4 *>(host.data() + off_items);
+  unsigned char *body = (unsigned char *)plan + kMultiPlanHeaderBytes;
+  DecodeSeq *hs = reinterpret_cast<DecodeSeq *>(body);
+  int4 *hi = reinterpret_cast<int4 *>(body + off_items);
   std::vector<int> order(n_seq);
   for (int i = 0; i < n_seq; ++i) order[i] = i;
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tiles[a] > tiles[b]; });
@@ -608,27 +623,86 @@ int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_he
         hi[n_items++] = make_int4(i, tok, sp, 0);
       }
   }
-  MultiDecodeArgs a;
+  // a fixed item count keeps the grid of a captured launch valid while the contexts grow:
+  // the padding items name no sequence and their CTAs leave at once
+  if (pad_items > 0) {
+    if (n_items > pad_items) return RD_ERR_LIMIT;
+    while (n_items < pad_items) hi[n_items++] = make_int4(-1, 0, 0, 0);
+  }
+  MultiDecodeArgs a;   // host pass: the tensor maps of every sequence, into its descriptor
   memset(&a, 0, sizeof(a));
   a.host_seqs = hs;
   a.n_seq = n_seq;
   a.n_head_kv = n_head_kv;
-  if ((rc = launch_decode_multi(k_type, v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
-  // The host vector is pageable: the copy has left it when cudaMemcpyAsync returns.
-  if (cudaMemcpyAsync(workspace, host.data(), off_items + (size_t)n_items * sizeof(int4),
+  if ((rc = launch_decode_multi(k_type, v_type, a, nullptr)) != RD_OK) return rc;
+  MultiPlanHeader h;
+  memset(&h, 0, sizeof(h));
+  h.magic = kMultiPlanMagic;
+  h.n_seq = n_seq;
+  h.q_len = q_len;
+  h.n_head = n_head;
+  h.n_head_kv = n_head_kv;
+  h.k_type = k_type;
+  h.v_type = v_type;
+  h.n_items = n_items;
+  h.max_items = max_items;
+  h.off_items = off_items;
+  h.copy_bytes = off_items + (size_t)n_items * sizeof(int4);
+  memcpy(plan, &h, sizeof(h));
+  return RD_OK;
+}
+
+int rd_attn_multi_launch(const void *plan, float scale, void *workspace, size_t workspace_bytes, void *stream) {
+  if (plan == nullptr) return RD_ERR_NULL;
+  MultiPlanHeader h;
+  memcpy(&h, plan, sizeof(h));
+  if (h.magic != kMultiPlanMagic || h.n_seq < 1 || h.n_items < 1 || h.n_items > h.max_items) return RD_ERR_SHAPE;
+  if (workspace == nullptr) return RD_ERR_WORKSPACE;
+  if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
+  int dev, rc;
+  if ((rc = current_device(&dev)) != RD_OK) return rc;
+  DeviceStatus *status = status_word(dev);   // every launch reports its bounded waits
+  if (status == nullptr) return RD_ERR_CUDA;
+  const size_t off_rec = h.off_items + align256((size_t)h.max_items * sizeof(int4));
+  const size_t need = off_rec + align256((size_t)h.max_items * h.n_head * kRec * sizeof(float));
+  if (workspace_bytes < need) return RD_ERR_WORKSPACE;
+  // From pageable memory the copy has left the plan when cudaMemcpyAsync returns; from
+  // pinned memory it reads the plan when the stream (or a replayed graph) reaches it.
+  if (cudaMemcpyAsync(workspace, (const unsigned char *)plan + kMultiPlanHeaderBytes, h.copy_bytes,
                       cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess)
     return RD_ERR_CUDA;
-  a.host_seqs = nullptr;
+  MultiDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n_seq = h.n_seq;
+  a.n_head_kv = h.n_head_kv;
   a.dev_seqs = reinterpret_cast<const DecodeSeq *>(workspace);
-  a.dev_items = reinterpret_cast<const int4 *>((const unsigned char *)workspace + off_items);
-  a.n_items = n_items;
-  a.q_len = q_len;
-  a.n_head = n_head;
+  a.dev_items = reinterpret_cast<const int4 *>((const unsigned char *)workspace + h.off_items);
+  a.n_items = h.n_items;
+  a.q_len = h.q_len;
+  a.n_head = h.n_head;
   a.scale = scale;
   a.records = reinterpret_cast<float *>((unsigned char *)workspace + off_rec);
   a.status = status;
-  if ((rc = launch_decode_multi(k_type, v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
-  return launch_merge_multi(a.dev_seqs, a.records, n_seq, q_len, n_head, (cudaStream_t)stream);
+  if ((rc = launch_decode_multi(h.k_type, h.v_type, a, (cudaStream_t)stream)) != RD_OK) return rc;
+  return launch_merge_multi(a.dev_seqs, a.records, h.n_seq, h.q_len, h.n_head, (cudaStream_t)stream);
+}
+
+int rd_attn_decode_multi(const rd_attn_seq *seqs, int n_seq, int q_len, int n_head, int n_head_kv,
+                         int head_dim, float scale, int k_type, int v_type, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+  if (n_seq < 0 || q_len < 1) {
+    const int rc = check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+    return rc != RD_OK ? rc : RD_ERR_SHAPE;
+  }
+  if (n_seq == 0) return check_attn_shape(n_head, n_head_kv, head_dim, k_type, v_type);
+  const size_t plan_bytes = rd_attn_multi_plan_bytes(n_seq, q_len);
+  if (plan_bytes == 0) return RD_ERR_CUDA;
+  // 16-byte aligned pageable plan of this call
+  std::vector<uint4> plan((plan_bytes + sizeof(uint4) - 1) / sizeof(uint4));
+  int rc = rd_attn_multi_plan(seqs, n_seq, q_len, n_head, n_head_kv, head_dim, k_type, v_type, 0, plan.data(),
+                              plan_bytes);
+  if (rc != RD_OK) return rc;
+  return rd_attn_multi_launch(plan.data(), scale, workspace, workspace_bytes, stream);
 }
 
 // ---- context-sharded decode with the exchange fused into the merge -------------------

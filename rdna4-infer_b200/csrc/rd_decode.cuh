@@ -710,6 +710,7 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
   float *rec0;
   if constexpr (MULTI) {
     const int4 item = p.items[blockIdx.x];
+    if (item.x < 0) return;   // padding of a plan with a fixed item count
     const DecodeSeq &d = p.seqs[item.x];
     qt = item.y;
     s = item.z;

@@ -148,3 +148,65 @@ def test_batched_decode_64_sequences(G, oracle, q_len):
         want = oracle.attn(G.host(qs[i]), G.host(kcs[i]), G.host(vcs[i]), pos, NKV, 1 / 16, 2, 1)
         check_attn(G.host(outs[i]), want, what=f"sequence {i} ({n} keys)")
     G.status_ok()
+
+
+def test_plan_and_launch_captured_with_a_growing_context(G, oracle):
+    """rd_attn_multi_plan into pinned memory + rd_attn_multi_launch captured ONCE: every
+    replay reads the plan as rewritten for that step (contexts one key longer each time,
+    item count padded to a fixed number), and matches the oracle."""
+    rd, lib = G.rd, G.lib
+    kt = vt = 3
+    rng = np.random.default_rng(77)
+    caps, t0 = [40, 700, 3000], [20, 650, 2900]
+    n = len(caps)
+    Ks = [rng.standard_normal((c, NKV, HD)).astype(np.float32) for c in caps]
+    Vs = [rng.standard_normal((c, NKV, HD)).astype(np.float32) for c in caps]
+    kcs = [oracle.kv_store_rows(kt, K) for K in Ks]
+    vcs = [oracle.kv_store_rows(vt, V) for V in Vs]
+    dks, dvs = [G.dev(k) for k in kcs], [G.dev(v) for v in vcs]
+    qs = [G.dev(rng.standard_normal((1, NH, HD)).astype(np.float32)) for _ in range(n)]
+    outs = [G.poison((1, NH, HD)) for _ in range(n)]
+    arr = (rd.AttnSeq * n)()
+    for i in range(n):
+        arr[i].q, arr[i].k, arr[i].v, arr[i].out = rd.ptr(qs[i]), rd.ptr(dks[i]), rd.ptr(dvs[i]), rd.ptr(outs[i])
+    pbytes = lib.rd_attn_multi_plan_bytes(n, 1)
+    assert pbytes > 256
+    plan = torch.empty(pbytes, dtype=torch.uint8).pin_memory()
+    wbytes = lib.rd_attn_multi_workspace_bytes(n, 1, NH, HD)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device="cuda")
+    pad = 64
+
+    def replan(step):
+        for i in range(n):
+            arr[i].t = t0[i] + step
+        rd.check(lib.rd_attn_multi_plan(C.addressof(arr), n, 1, NH, NKV, HD, kt, vt, pad, plan.data_ptr(), pbytes),
+                 "rd_attn_multi_plan")
+
+    replan(0)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        rd.check(lib.rd_attn_multi_launch(plan.data_ptr(), 1 / 16, rd.ptr(ws), wbytes, rd.stream_ptr()))   # warm-up
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        rd.check(lib.rd_attn_multi_launch(plan.data_ptr(), 1 / 16, rd.ptr(ws), wbytes, rd.stream_ptr()))
+    for step in (0, 1, 7, 19):
+        replan(step)
+        for o in outs:
+            o.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        for i in range(n):
+            t = t0[i] + step
+            q = G.host(qs[i])
+            want = oracle.attn(q, kcs[i], vcs[i], np.asarray([t], dtype=np.int32), NKV, 1 / 16, kt, vt)
+            check_attn(G.host(outs[i]), want, what=f"step {step}, sequence {i}")
+    G.status_ok()
+    # a plan that needs more items than the padding allows is refused, not truncated
+    assert lib.rd_attn_multi_plan(C.addressof(arr), n, 1, NH, NKV, HD, kt, vt, 2, plan.data_ptr(), pbytes) == rd.ERR_LIMIT
+    assert lib.rd_attn_multi_plan(C.addressof(arr), n, 1, NH, NKV, HD, kt, vt, pad, plan.data_ptr(), 128) == rd.ERR_WORKSPACE
+    assert lib.rd_attn_multi_launch(None, 1 / 16, rd.ptr(ws), wbytes, G.st()) == rd.ERR_NULL
+    bad = torch.zeros(pbytes, dtype=torch.uint8)
+    assert lib.rd_attn_multi_launch(bad.data_ptr(), 1 / 16, rd.ptr(ws), wbytes, G.st()) == rd.ERR_SHAPE
