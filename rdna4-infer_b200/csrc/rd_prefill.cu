@@ -140,6 +140,28 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   uint8_t *gQ = smem_raw;                                   // generic pointer to sQ
   const uint32_t bars = smem_u32(s_bars);
 
+  // Requested first, so that their latency runs under the set-up below: the positions of
+  // this tile's rows and -- where the tile is converted here -- all 16 query rows of the
+  // warp (32 float4 per lane; the conversion is bound by the latency of these loads).
+  int my_pos = -1;
+  if (threadIdx.x < 2 * kPfM) {
+    const int r = row0 + (threadIdx.x & (kPfM - 1));
+    if (r < p.n_q) my_pos = p.pos[r];
+  }
+  float4 qa[16], qb[16];
+  if (!p.q16 && warp < 8) {
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) {
+      const int gr = row0 + warp * 16 + rr;
+      qa[rr] = qb[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (gr < p.n_q) {
+        const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim);
+        qa[rr] = src[2 * lane];
+        qb[rr] = src[2 * lane + 1];
+      }
+    }
+  }
+
   if (threadIdx.x == 0) {
     s_maxpos = -1;
     s_abort = 0;
@@ -169,12 +191,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   __syncthreads();
   if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 1);   // barriers + TMEM allocated
 
-  // ---- positions of this tile's rows; the last key any of them attends ----
-  int my_pos = -1;
-  if (threadIdx.x < 2 * kPfM) {
-    const int r = row0 + (threadIdx.x & (kPfM - 1));
-    if (r < p.n_q) my_pos = p.pos[r];
-  }
+  // ---- the last key any row of this tile attends ----
   if (threadIdx.x < kPfM) {
     int mx = my_pos;
 #pragma unroll
@@ -194,7 +211,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   // ---- prologue: the Q tile as f16 in the swizzled K-major layout ----
   if (p.q16) {
     // rotated, scaled and rounded by q_prep_kernel: four TMA boxes of [128 rows][64 dims]
-    // (rows past n_q are filled with zeros)
+    // (rows past n_q are filled with zeros). Only this thread waits for that pass: the K
+    // and V producers are already loading.
     if (threadIdx.x == 0) {
       pdl_wait();   // that pass has completed (this launch may have started under it)
       const uint32_t full = bars + 8 * kBarQ;
@@ -204,20 +222,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         tma_load_2d(sQ + c * (kPfM * 128), &p.tm_q, head * kHeadDim + 64 * c, row0, full);
     }
   } else if (warp < 8) {
-    // f32 rows -> x scale * log2(e) -> f16, warps 0-7, 16 rows each. All 16 rows of the warp
-    // are requested before any is converted (32 float4 per lane): the conversion is bound
-    // by the latency of these loads, paid once this way.
-    float4 qa[16], qb[16];
-#pragma unroll
-    for (int rr = 0; rr < 16; ++rr) {
-      const int gr = row0 + warp * 16 + rr;
-      qa[rr] = qb[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (gr < p.n_q) {
-        const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)gr * p.n_head + head) * kHeadDim);
-        qa[rr] = src[2 * lane];
-        qb[rr] = src[2 * lane + 1];
-      }
-    }
+    // f32 rows -> x scale * log2(e) -> f16, warps 0-7, 16 rows each
 #pragma unroll
     for (int rr = 0; rr < 16; ++rr) {
       const int r = warp * 16 + rr;      // row inside the tile
