@@ -174,11 +174,10 @@ def prefill_leg(rd, torch, peaks):
 
         def call():
             s2 = rd.stream_ptr()
-            if fused:
-                rd.check(L.rd_kv_append(1, 1, rd.ptr(ks), rd.ptr(vs), rd.ptr(kc) + pos0 * row,
-                                        rd.ptr(vc) + pos0 * row, n_q, NKV, HD, rd.ptr(pos), 64, 1e7, s2))
-                rd.check(L.rd_attn_prefill_fused(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(gate),
-                                                 rd.ptr(pos), n_q, keys, NH, NKV, HD, SCALE, 64, 1e7, s2))
+            if fused:   # K/V append (K rotated), Q rotation, attention and gate: one call, two launches
+                rd.check(L.rd_attn_prefill_append_fused(rd.ptr(q), rd.ptr(ks), rd.ptr(vs), rd.ptr(kc), rd.ptr(vc),
+                                                        rd.ptr(o), rd.ptr(gate), rd.ptr(pos), n_q, pos0, keys, NH,
+                                                        NKV, HD, SCALE, 64, 1e7, s2))
             else:
                 rd.check(L.rd_fa2_prefill(rd.ptr(q), rd.ptr(kc), rd.ptr(vc), rd.ptr(o), rd.ptr(pos), n_q,
                                           keys - 1, keys, NH, NKV, HD, SCALE, s2))

@@ -381,6 +381,18 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
                           int head_dim, float scale, int n_rot, float freq_base, void *stream);
 
+/* The chunk's cache append fused in as well (f16 caches): rd_kv_append(k_new, v_new -> rows
+ * row0 .. row0 + n_q - 1, K rotated by pos[] when n_rot > 0; kv_store_row_launch,
+ * include/rdna4/kv.h:673-694, + rope_launch on k) and rd_attn_prefill_fused in one call. The
+ * pre-pass that rotates the queries stores the new rows too -- the (cos, sin) of a token
+ * are computed once for its 24 query and 4 key rows -- and writes the bytes rd_kv_append
+ * writes. k_new / v_new are [n_q][n_head_kv][head_dim] f32, 16-byte aligned;
+ * row0 + n_q <= keys_total. */
+int rd_attn_prefill_append_fused(const float *q, const float *k_new, const float *v_new, void *k, void *v,
+                                 float *o, const float *gate, const int32_t *pos, int n_q, int row0,
+                                 int keys_total, int n_head, int n_head_kv, int head_dim, float scale,
+                                 int n_rot, float freq_base, void *stream);
+
 /* ---- causal prefill over caches of ANY type pair on the tensor cores: what the reference
  * serves with its chunk path, attn_split_batch_launch (include/rdna4/attn.cuh:958-1049, all
  * 6 x 6 K x V types; dispatch src/graph.cuh:1486-1527), where every one of the n_q tokens

@@ -71,6 +71,7 @@ SIGNATURES = {
     "rd_fa2_prefill_usable": (_I, [_I, _I, _I, _I, _I, _I, _I]),
     "rd_fa2_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "rd_attn_prefill_fused": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _P]),
+    "rd_attn_prefill_append_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P]),
     "rd_attn_prefill_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I, _I, _I, _I]),
     "rd_attn_prefill_typed": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P,
                                    C.c_size_t, _P]),

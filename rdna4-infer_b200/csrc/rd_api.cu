@@ -879,7 +879,8 @@ int rd_fa2_prefill_usable(int k_type, int v_type, int n_q, int pos0, int n_head,
 static int prefill_common(const float *q, const void *k, const void *v, float *o, const float *gate,
                           const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv,
                           int head_dim, float scale, int n_rot, float freq_base, void *stream,
-                          void *records = nullptr, size_t record_bytes = 0) {
+                          void *records = nullptr, size_t record_bytes = 0, const float *k_new = nullptr,
+                          const float *v_new = nullptr, int row0 = 0) {
   int rc = check_attn_shape(n_head, n_head_kv, head_dim, RD_KV_F16, RD_KV_F16);
   if (rc != RD_OK) return rc;
   if (n_q < 1 || keys_total <= 0) return RD_ERR_SHAPE;
@@ -893,7 +894,7 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   if (status == nullptr) return RD_ERR_CUDA;
   // scratch: [rotated f16 queries, if the call rotates][key-split records, if any]
   int splits = prefill_splits(n_q, keys_total, n_head, sm_count(dev));
-  const size_t rope_need = n_rot > 0 ? align256(prefill_rope_bytes(n_q, n_head)) : 0;
+  const size_t rope_need = (n_rot > 0 || k_new != nullptr) ? align256(prefill_rope_bytes(n_q, n_head)) : 0;
   const size_t need = prefill_record_bytes(n_q, n_head, splits);
   if (records == nullptr && rope_need + (splits > 1 ? need : 0) > 0) {
     records = ensure_workspace(dev, rope_need + need);
@@ -903,8 +904,13 @@ static int prefill_common(const float *q, const void *k, const void *v, float *o
   void *rope_cs = rope_need > 0 ? records : nullptr;
   float *recs = (float *)((unsigned char *)records + rope_need);
   if (splits > 1 && record_bytes - rope_need < need) splits = 1;   // no room: one CTA per (token tile, head) walks all keys
+  // a fused append stores rows row0 .. row0 + n_q - 1 of the (f16) caches
+  const size_t row_bytes = (size_t)n_head_kv * kHeadDim * 2;
+  void *k_dst = k_new != nullptr ? (void *)((unsigned char *)const_cast<void *>(k) + (size_t)row0 * row_bytes) : nullptr;
+  void *v_dst = k_new != nullptr ? (void *)((unsigned char *)const_cast<void *>(v) + (size_t)row0 * row_bytes) : nullptr;
   return launch_prefill(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, scale, n_rot,
-                        freq_base, status, recs, splits, rope_cs, (cudaStream_t)stream);
+                        freq_base, status, recs, splits, rope_cs, k_new, v_new, k_dst, v_dst,
+                        (cudaStream_t)stream);
 }
 
 int rd_fa2_prefill(const float *q, const void *k, const void *v, float *o, const int32_t *pos,
@@ -920,6 +926,17 @@ int rd_attn_prefill_fused(const float *q, const void *k, const void *v, float *o
                           int head_dim, float scale, int n_rot, float freq_base, void *stream) {
   return prefill_common(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
                         n_rot, freq_base, stream);
+}
+
+int rd_attn_prefill_append_fused(const float *q, const float *k_new, const float *v_new, void *k, void *v,
+                                 float *o, const float *gate, const int32_t *pos, int n_q, int row0,
+                                 int keys_total, int n_head, int n_head_kv, int head_dim, float scale,
+                                 int n_rot, float freq_base, void *stream) {
+  if (k_new == nullptr || v_new == nullptr) return RD_ERR_NULL;
+  if (!aligned(k_new, 16) || !aligned(v_new, 16)) return RD_ERR_ALIGN;
+  if (row0 < 0 || n_q < 1 || (int64_t)row0 + n_q > keys_total) return RD_ERR_SHAPE;
+  return prefill_common(q, k, v, o, gate, pos, n_q, keys_total, n_head, n_head_kv, head_dim, scale,
+                        n_rot, freq_base, stream, nullptr, 0, k_new, v_new, row0);
 }
 
 // f16 copies of the caches that are not f16, then the key-split records

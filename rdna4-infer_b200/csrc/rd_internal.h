@@ -143,7 +143,7 @@ int encode_f16_tmap(void *tmap_out, const void *base, int n_head_kv, int64_t n_r
 // over gridDim.z and a second launch merges the per-split records.
 int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
                    const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
-                   int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits, void *q16,
+                   int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits, void *q16, const float *k_new, const float *v_new, void *k_dst, void *v_dst,
                    cudaStream_t st);
 size_t prefill_rope_bytes(int n_q, int n_head);   // the f16 query copy launch_prefill needs when n_rot > 0
 int prefill_splits(int n_q, int keys_total, int n_head, int sms);

@@ -98,6 +98,7 @@ struct PrefillArgs {
   float qscale;          // scale * log2(e)
   alignas(64) CUtensorMap tm_q;  // q16 != 0: the rotated, scaled f16 queries q_prep_kernel wrote
   int q16;               // 1: Q tile by TMA from tm_q; 0: converted from `q` (f32, no rotation) here
+  int kv_wait;           // 1: that pre-pass also stored cache rows: the K / V loads wait for it too
   int debug;             // timing experiments only (bit mask), 0 in production
   DeviceStatus *status;
   // Split over the keys (gridDim.z > 1): CTA (tile, head, z) walks only its share of the
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     // unit g = 2 j + u: keys of tile j, dims [128 u, 128 u + 128) as two 64-dim chunks, into
     // slot g % 3 -- one barrier per unit: the issuing thread pays for every wait and commit
     if (lane == 0) {
+      if (p.kv_wait) pdl_wait();   // the pre-pass of this call appended rows to the caches
       int slot = 0, use = 0;
       for (int g = 0; g < 2 * nt; ++g) {
         if (use > 0 && !mbar_wait(bars + 8 * (kBarKFree + slot), (use - 1) & 1, p.status, 11)) {
@@ -277,6 +279,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     // unit g = 2 j + u: keys [128 j + 64 u, + 64) of all 256 dims, into slot g % 2
     if (lane == 0) {
       bool ok = true;
+      if (p.kv_wait) pdl_wait();
       for (int g = 0; g < 2 * nt && ok; ++g) {
         const int slot = g & 1;
         if (g >= 2 && !mbar_wait(bars + 8 * (kBarVFree + slot), ((g >> 1) - 1) & 1, p.status, 22)) {
@@ -693,7 +696,9 @@ prefill_merge_kernel(const float *__restrict__ records, float *__restrict__ out,
 // after it as a programmatic dependent launch.
 __global__ void __launch_bounds__(256)
 q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int n_head, int n_rot, float qscale,
-              uint4 *__restrict__ q16, const __grid_constant__ RopeTable tab) {
+              uint4 *__restrict__ q16, const float *__restrict__ k_new, const float *__restrict__ v_new,
+              uint4 *__restrict__ k_dst, uint4 *__restrict__ v_dst, int nkv,
+              const __grid_constant__ RopeTable tab) {
   __shared__ float2 s_cs[32];
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -724,6 +729,30 @@ q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int 
     }
     q16[row * 32 + lane] = make_uint4(pack_h2(v[0] * qscale, v[1] * qscale), pack_h2(v[2] * qscale, v[3] * qscale),
                                       pack_h2(v[4] * qscale, v[5] * qscale), pack_h2(v[6] * qscale, v[7] * qscale));
+  }
+  // Fused append (k_new != nullptr): the token's K rows, rotated with the same (cos, sin) and
+  // the operation order of kv_append_kernel, and its V rows, rounded to f16 into cache row t
+  // -- the bytes rd_kv_append stores for f16 caches.
+  if (k_new == nullptr) return;
+  for (int r = warp; r < 2 * nkv; r += 8) {
+    const bool is_k = r < nkv;
+    const size_t row = (size_t)t * nkv + (is_k ? r : r - nkv);
+    const float4 *src = reinterpret_cast<const float4 *>((is_k ? k_new : v_new) + row * kHeadDim);
+    const float4 a = src[2 * lane], b = src[2 * lane + 1];
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    if (is_k) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], half_lanes);
+        if (rot) {
+          const float2 cs = s_cs[8 * (lo ? lane : lane - half_lanes) + i];
+          v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y))
+                    : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x));
+        }
+      }
+    }
+    (is_k ? k_dst : v_dst)[row * 32 + lane] =
+        make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
   }
 }
 size_t prefill_rope_bytes(int n_q, int n_head) { return (size_t)n_q * n_head * kHeadDim * 2; }
@@ -758,7 +787,8 @@ size_t prefill_record_bytes(int n_q, int n_head, int splits) {
 int launch_prefill(const float *q, const void *k, const void *v, float *out, const float *gate,
                    const int32_t *pos, int n_q, int keys_total, int n_head, int n_head_kv, float scale,
                    int n_rot, float freq_base, DeviceStatus *status, float *records, int n_splits,
-                   void *q16, cudaStream_t st) {
+                   void *q16, const float *k_new, const float *v_new, void *k_dst, void *v_dst,
+                   cudaStream_t st) {
   PrefillArgs a;
   memset(&a, 0, sizeof(a));
   int rc = encode_f16_tmap(&a.tm_k, k, n_head_kv, keys_total, kPfN);
@@ -773,8 +803,10 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   a.n_head = n_head;
   a.nkv = n_head_kv;
   a.qscale = scale * 1.4426950408889634f;
-  a.q16 = n_rot > 0 ? 1 : 0;
-  if (n_rot > 0) {
+  const bool prepass = n_rot > 0 || k_new != nullptr;   // rotation and / or fused append
+  a.q16 = prepass ? 1 : 0;
+  a.kv_wait = k_new != nullptr ? 1 : 0;
+  if (prepass) {
     if (q16 == nullptr) return RD_ERR_WORKSPACE;
     if ((rc = encode_f16_tmap(&a.tm_q, q16, n_head, n_q, kPfM)) != RD_OK) return rc;
   }
@@ -795,8 +827,9 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   if (n_splits < 1 || records == nullptr) n_splits = 1;
   a.records = records;
   const dim3 grid((unsigned)((n_q + kPfM - 1) / kPfM), (unsigned)n_head, (unsigned)n_splits);
-  if (n_rot > 0) {
-    q_prep_kernel<<<(unsigned)n_q, 256, 0, st>>>(q, pos, n_head, n_rot, a.qscale, (uint4 *)q16,
+  if (prepass) {
+    q_prep_kernel<<<(unsigned)n_q, 256, 0, st>>>(q, pos, n_head, n_rot, a.qscale, (uint4 *)q16, k_new, v_new,
+                                                (uint4 *)k_dst, (uint4 *)v_dst, n_head_kv,
                                                 make_rope_table(n_rot, freq_base));
     if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
     // the tile kernel may start while that pass runs; it waits for it (griddepcontrol)

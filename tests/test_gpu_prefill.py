@@ -136,3 +136,56 @@ def test_typed_prefill_over_quantized_caches(G, oracle, rd, kt, vt, pos0):
         assert rd.lib.rd_attn_prefill_typed(rd.ptr(dq), rd.ptr(dk), rd.ptr(dv), rd.ptr(out), None, rd.ptr(dpos), n_q,
                                             keys_total, nh, nkv, 256, 1 / 16, kt, vt, 0, 0.0, rd.ptr(ws), nbytes - 256,
                                             G.st()) == rd.ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("n_q,row0,n_rot,with_gate", [(512, 0, 64, True), (200, 300, 64, False), (130, 70, 0, True),
+                                                      (1, 0, 32, False)])
+def test_prefill_with_the_append_fused(G, oracle, rd, n_q, row0, n_rot, with_gate):
+    """rd_attn_prefill_append_fused = rd_kv_append (rows row0.., K rotated) + rd_attn_prefill_fused:
+    the caches end up with the bytes rd_kv_append writes, the output is the two-call chain's
+    (same cache bytes, same query path: bit-identical) and passes the oracle gate."""
+    import torch
+    rng = np.random.default_rng(n_q + row0)
+    nh, nkv = 24, 4
+    keys_total = row0 + n_q
+    q = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    ks = rng.standard_normal((n_q, nkv, 256)).astype(np.float32)
+    vs = rng.standard_normal((n_q, nkv, 256)).astype(np.float32)
+    gate = rng.standard_normal((n_q, nh, 256)).astype(np.float32) if with_gate else None
+    pos = np.arange(row0, keys_total, dtype=np.int32)
+    old = oracle.kv_store_rows(1, rng.standard_normal((max(row0, 1), nkv, 256)).astype(np.float32))[:row0 * nkv * 512]
+    base_k = np.concatenate([old, np.full(n_q * nkv * 512, 0xEE, dtype=np.uint8)])
+    old_v = oracle.kv_store_rows(1, rng.standard_normal((max(row0, 1), nkv, 256)).astype(np.float32))[:row0 * nkv * 512]
+    base_v = np.concatenate([old_v, np.full(n_q * nkv * 512, 0xEE, dtype=np.uint8)])
+    dq, dks, dvs, dpos = G.dev(q), G.dev(ks), G.dev(vs), G.dev(pos)
+    dg = G.dev(gate) if with_gate else None
+    # two calls
+    kc1, vc1 = G.dev(base_k), G.dev(base_v)
+    off = row0 * nkv * 512
+    rd.check(rd.lib.rd_kv_append(1, 1, rd.ptr(dks), rd.ptr(dvs), rd.ptr(kc1) + off, rd.ptr(vc1) + off, n_q, nkv, 256,
+                                 rd.ptr(dpos) if n_rot else None, n_rot, 1e7, G.st()))
+    out1 = G.poison(q.shape)
+    rd.check(rd.lib.rd_attn_prefill_fused(rd.ptr(dq), rd.ptr(kc1), rd.ptr(vc1), rd.ptr(out1), rd.ptr(dg), rd.ptr(dpos),
+                                          n_q, keys_total, nh, nkv, 256, 1 / 16, n_rot, 1e7, G.st()))
+    # one call
+    kc2, vc2 = G.dev(base_k), G.dev(base_v)
+    out2 = G.poison(q.shape)
+    rd.check(rd.lib.rd_attn_prefill_append_fused(rd.ptr(dq), rd.ptr(dks), rd.ptr(dvs), rd.ptr(kc2), rd.ptr(vc2),
+                                                 rd.ptr(out2), rd.ptr(dg), rd.ptr(dpos), n_q, row0, keys_total, nh,
+                                                 nkv, 256, 1 / 16, n_rot, 1e7, G.st()))
+    torch.cuda.synchronize()
+    assert rd.lib.rd_device_status() == rd.OK
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(out1, out2)
+    # and the chain against the oracle
+    qr = oracle.rope(q, pos, n_rot=n_rot) if n_rot else q
+    att = oracle.attn(qr, G.host(kc2), G.host(vc2), pos, nkv, 1 / 16, 1, 1)
+    want = oracle.sigmoid_gate(gate.copy(), att)[1] if with_gate else att
+    check_attn(G.host(out2), want, what=f"append-fused prefill n_q={n_q} row0={row0} n_rot={n_rot}")
+    # argument errors
+    call = lambda kn, r0, kt_: rd.lib.rd_attn_prefill_append_fused(rd.ptr(dq), kn, rd.ptr(dvs), rd.ptr(kc2),
+                                                                   rd.ptr(vc2), rd.ptr(out2), None, rd.ptr(dpos), n_q,
+                                                                   r0, kt_, nh, nkv, 256, 1 / 16, n_rot, 1e7, G.st())
+    assert call(None, row0, keys_total) == rd.ERR_NULL
+    assert call(rd.ptr(dks), row0 + 1, keys_total) == rd.ERR_SHAPE
+    assert call(rd.ptr(dks), -1, keys_total) == rd.ERR_SHAPE
