@@ -436,7 +436,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--fused-append", action="store_true", help=argparse.SUPPRESS)
+    # comparison aid: the three-launch layer-step (append, decode, merge)
+    ap.add_argument("--separate-append", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"], help=argparse.SUPPRESS)
     # profiling aid: W warm-up steps only (no 300 ms floor) and no extra rounds, so that a
     # capture under ncu sees few launches before the one it wants
@@ -541,7 +542,7 @@ def main():
     def layer_step(l, host_io):
         st = rd.stream_ptr()   # the capturing stream while a graph is being recorded
         n = 0
-        if world == 1 and args.fused_append:    # two launches per layer-step instead of three
+        if world == 1 and not args.separate_append:    # two launches per layer-step instead of three
             rd.check(L.rd_attn_decode_append_ws(rd.ptr(q_dev[l]), rd.ptr(knew_dev[l]), rd.ptr(vnew_dev[l]),
                                                 rd.ptr(kcache[l]), rd.ptr(vcache[l]), rd.ptr(o_dev[l]), POS, NH,
                                                 NKV, HD, SCALE, KT, VT, rd.ptr(gate_dev[l]), rd.ptr(ws), ws_bytes,
@@ -783,6 +784,9 @@ def main():
                          "e2e_mean": bytes_step * K * ROUNDS / (sum(r_e2e) * 1e-3) / 1e9,
                          "e2e_best": bytes_step * K / (min(r_e2e) * 1e-3) / 1e9}
     out["config"]["exchange"] = exchange
+    out["config"]["layer_step"] = ("append, decode, merge: three launches" if world == 1 and args.separate_append else
+                                   "decode with the new row's append fused + merge: two launches" if world == 1 else
+                                   "one launch per rank (the owner of the newest position appends in it)")
     if rank == 0 and world == 1 and args.leg == "all":
         out["prefill"] = prefill_leg(rd, torch, peaks)
     if rank == 0 and world == 1 and args.leg == "all":
