@@ -656,7 +656,11 @@ int rd_attn_multi_launch(const void *plan, float scale, void *workspace, size_t 
   if (plan == nullptr) return RD_ERR_NULL;
   MultiPlanHeader h;
   memcpy(&h, plan, sizeof(h));
-  if (h.magic != kMultiPlanMagic || h.n_seq < 1 || h.n_items < 1 || h.n_items > h.max_items) return RD_ERR_SHAPE;
+  if (h.magic != kMultiPlanMagic || h.n_seq < 1 || h.q_len < 1 || h.n_items < 1 || h.n_items > h.max_items ||
+      h.off_items != align256((size_t)h.n_seq * sizeof(DecodeSeq)) ||
+      h.copy_bytes != h.off_items + (size_t)h.n_items * sizeof(int4) ||
+      check_attn_shape(h.n_head, h.n_head_kv, kHeadDim, h.k_type, h.v_type) != RD_OK)
+    return RD_ERR_SHAPE;   // not a plan of rd_attn_multi_plan, or damaged
   if (workspace == nullptr) return RD_ERR_WORKSPACE;
   if (!aligned(workspace, 256)) return RD_ERR_ALIGN;
   int dev, rc;
