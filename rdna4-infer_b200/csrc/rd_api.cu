@@ -980,14 +980,20 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
   unsigned char *w = (unsigned char *)workspace;
   const void *k16 = k, *v16 = v;
   cudaStream_t st = (cudaStream_t)stream;
+  void *kdst = nullptr, *vdst = nullptr;
   if (k_type != RD_KV_F16) {
-    if ((rc = launch_kv_dequant_f16(k_type, k, w, n_values, st)) != RD_OK) return rc;
+    kdst = w;
     k16 = w;
     w += align256((size_t)n_values * 2);
   }
   if (v_type != RD_KV_F16) {
-    if ((rc = launch_kv_dequant_f16(v_type, v, w, n_values, st)) != RD_OK) return rc;
+    vdst = w;
     v16 = w;
+  }
+  if (kdst != nullptr || vdst != nullptr) {   // one launch for both tensors
+    if ((rc = launch_kv_dequant_f16_pair(k_type, kdst != nullptr ? k : nullptr, kdst, v_type,
+                                         vdst != nullptr ? v : nullptr, vdst, n_values, st)) != RD_OK)
+      return rc;
   }
   // what follows the copies holds the key-split records (never the library's own workspace:
   // this entry allocates nothing)

@@ -22,6 +22,8 @@ int launch_sigmoid_gate(float *g, float *y, int64_t n, cudaStream_t st);
 // n_values stored values of `type` at src -> f16 at dst (the dequantizing loads of
 // include/rdna4/kv.h:174-368, rounded once).
 int launch_kv_dequant_f16(int type, const void *src, void *dst, int64_t n_values, cudaStream_t st);
+int launch_kv_dequant_f16_pair(int kt, const void *k, void *kdst, int vt, const void *v, void *vdst,
+                               int64_t n_values, cudaStream_t st);
 
 // ---- rd_pre.cu
 int launch_rms_norm(const float *x, const float *w, float *y, int64_t nrows, int64_t ncols, float eps,

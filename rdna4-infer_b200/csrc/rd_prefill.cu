@@ -84,6 +84,7 @@ constexpr uint32_t kTmemO = 0;            // columns [0, 256): output accumulato
 constexpr uint32_t kTmemS = 256;          // columns [256, 512): two score buffers of 128; the
                                           // f16 P of a tile overwrites its first 64 columns
 constexpr float kLazyThreshold = 8.0f;    // log2 units
+constexpr int kPfMaxSplits = 8;           // key splits per (token tile, head) at most
 
 struct PrefillArgs {
   alignas(64) CUtensorMap tm_k;
@@ -122,6 +123,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
   __shared__ float s_ref[2][kPfM];     // [tile parity][row]: the reference maximum that tile left
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();   // the merge pass of a key split may be scheduled under this kernel
   if (threadIdx.x == 0) RD_PF_TRACE(0, 47, 0);   // kernel entry
   const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) tiles first
   const int head = blockIdx.y;
@@ -656,31 +658,48 @@ prefill_merge_kernel(const float *__restrict__ records, float *__restrict__ out,
                      int64_t n_rows, int n_splits) {
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 6);
   const int tx = threadIdx.x & 63;
+  pdl_wait();   // launched under the tile kernel: its records are complete from here on
   if (row >= n_rows) return;
   const float *rec = records + (size_t)row * n_splits * kRec;
+  // every load of the row is requested before the first is used (at most kPfMaxSplits
+  // records): one round trip to L2 instead of one for the maxima and one per record
+  float m[kPfMaxSplits], lz[kPfMaxSplits];
+  float2 va[kPfMaxSplits], vb[kPfMaxSplits];
+#pragma unroll
+  for (int z = 0; z < kPfMaxSplits; ++z) {
+    m[z] = -INFINITY;
+    lz[z] = 0.f;
+    va[z] = vb[z] = make_float2(0.f, 0.f);
+    if (z < n_splits) {
+      const float *r = rec + (size_t)z * kRec;
+      m[z] = __ldcg(r);
+      lz[z] = __ldcg(r + 1);
+      va[z] = __ldcg(reinterpret_cast<const float2 *>(r + 2 + 4 * tx));   // a record's values start 8 bytes
+      vb[z] = __ldcg(reinterpret_cast<const float2 *>(r + 4 + 4 * tx));   // into a 16-byte line
+    }
+  }
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (gate != nullptr) g = *reinterpret_cast<const float4 *>(gate + (size_t)row * kHeadDim + 4 * tx);
   float mm = -INFINITY;
-  for (int z = 0; z < n_splits; ++z) mm = fmaxf(mm, rec[(size_t)z * kRec]);
+#pragma unroll
+  for (int z = 0; z < kPfMaxSplits; ++z) mm = fmaxf(mm, m[z]);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float l = 0.f;
   if (mm != -INFINITY) {
-    for (int z = 0; z < n_splits; ++z) {
-      const float *r = rec + (size_t)z * kRec;
-      const float m = r[0];
-      if (m == -INFINITY) continue;
-      const float w = __expf(m - mm);
-      l = fmaf(r[1], w, l);
-      const float2 a = *reinterpret_cast<const float2 *>(r + 2 + 4 * tx);
-      const float2 b = *reinterpret_cast<const float2 *>(r + 4 + 4 * tx);
-      acc.x = fmaf(a.x, w, acc.x);
-      acc.y = fmaf(a.y, w, acc.y);
-      acc.z = fmaf(b.x, w, acc.z);
-      acc.w = fmaf(b.y, w, acc.w);
+#pragma unroll
+    for (int z = 0; z < kPfMaxSplits; ++z) {
+      if (m[z] == -INFINITY) continue;
+      const float w = __expf(m[z] - mm);
+      l = fmaf(lz[z], w, l);
+      acc.x = fmaf(va[z].x, w, acc.x);
+      acc.y = fmaf(va[z].y, w, acc.y);
+      acc.z = fmaf(vb[z].x, w, acc.z);
+      acc.w = fmaf(vb[z].y, w, acc.w);
     }
   }
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   float4 o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
   if (gate != nullptr) {
-    const float4 g = *reinterpret_cast<const float4 *>(gate + (size_t)row * kHeadDim + 4 * tx);
     o.x *= __fdividef(1.0f, 1.0f + __expf(-g.x));
     o.y *= __fdividef(1.0f, 1.0f + __expf(-g.y));
     o.z *= __fdividef(1.0f, 1.0f + __expf(-g.z));
@@ -772,7 +791,7 @@ int prefill_splits(int n_q, int keys_total, int n_head, int sms) {
   };
   int best = 1;
   double best_cost = cost(1) * 0.92;   // a split must win clearly to be worth its records
-  for (int z = 2; z <= 8 && tiles / z >= 8; ++z) {
+  for (int z = 2; z <= kPfMaxSplits && tiles / z >= 8; ++z) {
     if (cost(z) < best_cost) {
       best_cost = cost(z);
       best = z;
@@ -851,8 +870,19 @@ int launch_prefill(const float *q, const void *k, const void *v, float *out, con
   }
   if (n_splits > 1) {
     const int64_t n_rows = (int64_t)n_q * n_head;
-    prefill_merge_kernel<<<(unsigned)((n_rows + 3) / 4), 256, 0, st>>>(records, out, gate, n_rows, n_splits);
-    if (cudaGetLastError() != cudaSuccess) return RD_ERR_CUDA;
+    if (n_splits > kPfMaxSplits) return RD_ERR_SHAPE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((n_rows + 3) / 4));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, prefill_merge_kernel, (const float *)records, out, gate, n_rows, n_splits) !=
+        cudaSuccess)
+      return RD_ERR_CUDA;
   }
   return RD_OK;
 }
