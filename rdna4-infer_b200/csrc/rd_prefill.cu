@@ -584,6 +584,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         sts128(stg + r * 256 + ((q ^ (r & 15)) << 4), w[0], w[1], w[2], w[3]);
       }
       asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
+      if (threadIdx.x == 0) RD_PF_TRACE(1, 47, 2 + cc);   // round cc staged
       // 128 threads: 8 rows x 16 chunks per pass
       if (rec_mode) {
 #pragma unroll 8
@@ -639,6 +640,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
         }
       }
       asm volatile("bar.sync %0, 128;" ::"r"(3 + ch) : "memory");
+      if (threadIdx.x == 0) RD_PF_TRACE(1, 47, cc);   // round cc stored
     }
   }
   tc_fence_before();
