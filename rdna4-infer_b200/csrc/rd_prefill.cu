@@ -787,6 +787,12 @@ size_t prefill_rope_bytes(int n_q, int n_head) { return (size_t)n_q * n_head * k
 int prefill_splits(int n_q, int keys_total, int n_head, int sms) {
   const int ctas = ((n_q + kPfM - 1) / kPfM) * n_head;
   const int tiles = (keys_total + kPfN - 1) / kPfN;
+#ifdef RD_TIMING_SWITCHES
+  if (const char *e = getenv("RD_PF_SPLITS")) {   // timing builds: force a split count
+    const int z = atoi(e);
+    if (z >= 1 && z <= kPfMaxSplits && z <= tiles) return z;
+  }
+#endif
   auto cost = [&](int z) {
     const double waves = (double)((ctas * z + sms - 1) / sms);
     return waves * ((double)tiles / z * 2.0 + 9.0) + (z > 1 ? 0.0005 * n_q * n_head * z : 0.0);
