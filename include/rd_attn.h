@@ -413,7 +413,7 @@ int rd_attn_prefill_typed(const float *q, const void *k, const void *v, float *o
  * Synchronises the device; meant for tests and debugging, not for the hot path. */
 int rd_device_status(void);
 /* Which wait gave up, for the last RD_ERR_DEVICE that rd_device_status returned: a small
- * site number from the kernel sources (prefill 11-22, decode 1-9 and 90, exchange 100 +
+ * site number from the kernel sources (prefill 11-23, decode 1-9 and 90, exchange 100 +
  * rank); 0 if none was ever reported. For bug reports. */
 int rd_device_timeout_site(void);
 

@@ -530,6 +530,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const __grid_con
     tc_fence_after();
   }
 
+  // With the queries coming from the pre-pass, nothing may be stored before that pass has
+  // completed: o may alias q, which it is still reading. A CTA with key tiles knows this from
+  // its Q tile; one without (no row attends a key) waits for the tile here -- its TMA load was
+  // issued behind the dependency wait all the same.
+  if (p.q16 && nt == 0 && threadIdx.x == 0 && !mbar_wait(bars + 8 * kBarQ, 0, p.status, 23)) s_abort = 1;
   __syncthreads();
   const bool aborted = s_abort != 0;
   // the two sets' row sums, each with the reference it is expressed in: [set][sum,

@@ -189,3 +189,21 @@ def test_prefill_with_the_append_fused(G, oracle, rd, n_q, row0, n_rot, with_gat
     assert call(None, row0, keys_total) == rd.ERR_NULL
     assert call(rd.ptr(dks), row0 + 1, keys_total) == rd.ERR_SHAPE
     assert call(rd.ptr(dks), -1, keys_total) == rd.ERR_SHAPE
+
+
+def test_rotating_prefill_in_place_with_a_tile_that_attends_nothing(G, oracle, rd):
+    """o aliases q, the queries are rotated by the pre-pass, and the first token tile has no
+    key at all (pos = -1): that tile's CTAs have nothing to wait for but must not store their
+    zeros before the pre-pass has read the rows they overwrite."""
+    rng = np.random.default_rng(11)
+    n_q, nh, nkv, keys_total = 256, 24, 4, 128
+    K = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    V = rng.standard_normal((keys_total, nkv, 256)).astype(np.float32)
+    q = rng.standard_normal((n_q, nh, 256)).astype(np.float32)
+    kc, vc = oracle.kv_store_rows(1, K), oracle.kv_store_rows(1, V)
+    pos = np.concatenate([np.full(128, -1), np.arange(128)]).astype(np.int32)
+    want = oracle.attn(oracle.rope(q, np.maximum(pos, 0)), kc, vc, pos, nkv, 1 / 16, 1, 1)
+    for _ in range(3):
+        got = run_prefill(G, rd, q, kc, vc, pos, keys_total, nkv, n_rot=64, inplace=True)
+        assert (got[:128] == 0).all()
+        check_attn(got, want, what="in-place rotating prefill, key-less first tile")
