@@ -729,6 +729,27 @@ q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int 
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pairs = n_rot / 2;
+  // a warp has at most three head rows (n_head <= 24): requested before the table is
+  // computed, so that their latency and the sincosf run side by side
+  float4 pa[3], pb[3];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int head = warp + 8 * j;
+    pa[j] = pb[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (head < n_head) {
+      const float4 *src = reinterpret_cast<const float4 *>(q + ((size_t)t * n_head + head) * kHeadDim);
+      pa[j] = src[2 * lane];
+      pb[j] = src[2 * lane + 1];
+    }
+  }
+  // ... and, with a fused append, the warp's K or V row of the token (2 * nkv <= 8 rows)
+  float4 ka = make_float4(0.f, 0.f, 0.f, 0.f), kb = ka;
+  if (k_new != nullptr && warp < 2 * nkv) {
+    const float4 *src = reinterpret_cast<const float4 *>((warp < nkv ? k_new : v_new) +
+                                                         ((size_t)t * nkv + (warp < nkv ? warp : warp - nkv)) * kHeadDim);
+    ka = src[2 * lane];
+    kb = src[2 * lane + 1];
+  }
   if ((int)threadIdx.x < pairs) {
     float c, s;
     sincosf((float)pos[t] * tab.f[threadIdx.x], &s, &c);
@@ -739,10 +760,12 @@ q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int 
   // l ^ (n_rot/16) at the same element index
   const int half_lanes = n_rot / 16;
   const bool rot = lane < 2 * half_lanes, lo = lane < half_lanes;
-  for (int head = warp; head < n_head; head += 8) {
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int head = warp + 8 * j;
+    if (head >= n_head) break;
     const size_t row = (size_t)t * n_head + head;
-    const float4 *src = reinterpret_cast<const float4 *>(q + row * kHeadDim);
-    const float4 a = src[2 * lane], b = src[2 * lane + 1];
+    const float4 a = pa[j], b = pb[j];
     float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -759,13 +782,12 @@ q_prep_kernel(const float *__restrict__ q, const int32_t *__restrict__ pos, int 
   // Fused append (k_new != nullptr): the token's K rows, rotated with the same (cos, sin) and
   // the operation order of kv_append_kernel, and its V rows, rounded to f16 into cache row t
   // -- the bytes rd_kv_append stores for f16 caches.
-  if (k_new == nullptr) return;
-  for (int r = warp; r < 2 * nkv; r += 8) {
+  if (k_new == nullptr || warp >= 2 * nkv) return;
+  {
+    const int r = warp;
     const bool is_k = r < nkv;
     const size_t row = (size_t)t * nkv + (is_k ? r : r - nkv);
-    const float4 *src = reinterpret_cast<const float4 *>((is_k ? k_new : v_new) + row * kHeadDim);
-    const float4 a = src[2 * lane], b = src[2 * lane + 1];
-    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
     if (is_k) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
