@@ -148,6 +148,12 @@ int rd_pre_attn_fused(const float *q_gate, const float *k_src, const float *v_sr
  * splits than key tiles). Any output pointer may be NULL. Host arithmetic only when
  * sm_count is given. */
 int rd_attn_splits_for(int n_keys, int k_type, int v_type, int n_head, int forced);
+/* What the prefill entries do with a chunk of n_q tokens over keys_total keys on a GPU of
+ * sm_count SMs (<= 0: the current device): the key splits per (128-token tile, head) and
+ * the CTAs of the tile-kernel launch. One split unless the cost model says that filling the
+ * idle SMs outweighs a second wave of fixed costs and the records (from about 8192 keys for
+ * 512 tokens x 24 heads on 148 SMs). Host arithmetic only when sm_count is given. */
+int rd_attn_prefill_plan(int n_q, int keys_total, int n_head, int sm_count, int *n_splits, int *n_ctas);
 int rd_attn_plan(int n_keys, int n_tok, int n_head_kv, int k_type, int v_type, int sm_count,
                  int *tile_keys, int *ring_stages, int *n_splits);
 

@@ -43,6 +43,7 @@ SIGNATURES = {
     "rd_pre_attn_fused": (_I, [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I,
                                _F, _P]),
     "rd_attn_splits_for": (_I, [_I, _I, _I, _I, _I]),
+    "rd_attn_prefill_plan": (_I, [_I, _I, _I, _I, _P, _P]),
     "rd_attn_plan": (_I, [_I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "rd_attn_partial_bytes": (C.c_size_t, [_I, _I, _I]),
     "rd_attn_workspace_bytes": (C.c_size_t, [_I, _I, _I]),

@@ -392,6 +392,20 @@ int rd_attn_plan(int n_keys, int n_tok, int n_head_kv, int k_type, int v_type, i
   return RD_OK;
 }
 
+int rd_attn_prefill_plan(int n_q, int keys_total, int n_head, int sm_count, int *n_splits, int *n_ctas) {
+  if (n_q < 1 || keys_total < 1 || n_head < 1) return RD_ERR_SHAPE;
+  if (sm_count <= 0) {
+    int dev;
+    const int rc = current_device(&dev);
+    if (rc != RD_OK) return rc;
+    sm_count = ::sm_count(dev);
+  }
+  const int z = prefill_splits(n_q, keys_total, n_head, sm_count);
+  if (n_splits != nullptr) *n_splits = z;
+  if (n_ctas != nullptr) *n_ctas = ((n_q + 127) / 128) * n_head * z;
+  return RD_OK;
+}
+
 size_t rd_attn_partial_bytes(int n_head, int head_dim, int n_splits) {
   if (n_head < 0 || head_dim < 0 || n_splits < 0) return 0;
   return (size_t)n_head * (size_t)n_splits * (2 + (size_t)head_dim) * sizeof(float);

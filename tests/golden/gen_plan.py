@@ -38,6 +38,12 @@ def table():
             lines.append(f"{NAMES[kt]} {NAMES[vt]} | {tile.value} {stages.value} | "
                          + " ".join(map(str, s1)) + " | " + " ".join(map(str, s4)) + " | "
                          + " ".join(map(str, ref)))
+    lines.append("# prefill plan on 148 SMs, 24 heads: n_q keys_total | key splits, CTAs of the tile-kernel launch")
+    for n_q, keys in ((1, 1), (200, 200), (512, 512), (512, 2048), (512, 4096), (512, 8192), (512, 16384),
+                      (512, 131072), (2048, 8192), (8192, 8192), (130, 4130)):
+        z, ctas = C.c_int(), C.c_int()
+        rd.check(L.rd_attn_prefill_plan(n_q, keys, 24, 148, C.addressof(z), C.addressof(ctas)))
+        lines.append(f"{n_q} {keys} | {z.value} {ctas.value}")
     return "\n".join(lines) + "\n"
 
 

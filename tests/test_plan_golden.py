@@ -47,3 +47,24 @@ def test_plan_properties():
     assert L.rd_attn_plan(10, 1, 3, 3, 3, 148, None, None, None) == rd.ERR_UNSUPPORTED
     assert L.rd_attn_plan(10, 0, 4, 3, 3, 148, None, None, None) == rd.ERR_SHAPE
     assert L.rd_attn_plan(10, 1, 4, 3, 3, 148, None, None, None) == rd.OK
+
+
+def test_prefill_plan_properties():
+    """rd_attn_prefill_plan: one split unless filling the idle SMs pays; never more CTAs than
+    two waves' worth for the reference's FA2 window; argument errors."""
+    rd = importlib.import_module("rdna4-infer_b200")
+    L = rd.lib
+    z, ctas = C.c_int(), C.c_int()
+    plan = lambda n_q, keys, sms=148: (L.rd_attn_prefill_plan(n_q, keys, 24, sms, C.addressof(z), C.addressof(ctas)),
+                                       z.value, ctas.value)
+    assert plan(512, 512) == (0, 1, 96) and plan(512, 4096) == (0, 1, 96)
+    assert plan(512, 8192) == (0, 3, 288)                       # 96 -> 288 CTAs: two full waves of 148 SMs
+    assert plan(8192, 8192) == (0, 1, 64 * 24)                  # enough token tiles already
+    for keys in (1, 127, 128, 129, 1000, 5000, 100000):
+        rc, s, c = plan(512, keys)
+        assert rc == 0 and 1 <= s <= 8 and c == 4 * 24 * s
+        assert s == 1 or (keys + 127) // 128 // s >= 8          # a split keeps at least 8 tiles per CTA
+    assert plan(512, 8192, 96)[1] == 1                          # 96 SMs are full with one wave
+    assert L.rd_attn_prefill_plan(0, 10, 24, 148, None, None) == rd.ERR_SHAPE
+    assert L.rd_attn_prefill_plan(10, 0, 24, 148, None, None) == rd.ERR_SHAPE
+    assert L.rd_attn_prefill_plan(10, 10, 24, 148, None, None) == rd.OK
