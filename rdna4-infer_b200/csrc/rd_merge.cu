@@ -50,6 +50,32 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     hi = n_in;
   }
 
+  // One pass: group ty walks records lo+ty, lo+ty+16, ... and keeps a local log-sum-exp
+  // (m, l, acc); the 16 groups are then combined through shared memory. An empty record
+  // (m = -inf) weighs nothing and whatever its body holds is never used. A batch is ten
+  // records per group -- the 148 records of a full-GPU decode in ONE round trip to L2 (four
+  // per batch took three) -- and the first batch is requested before anything else, the
+  // gate value with it.
+  constexpr int kBatch = 10;
+  float mB[kBatch], aB[kBatch], lB[kBatch];
+  auto request = [&](int s0) {
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const int s = s0 + k * kMergeGroups;
+      mB[k] = -INFINITY;
+      aB[k] = lB[k] = 0.f;
+      if (s < hi) {
+        const float *rec = base + (size_t)s * kRec;
+        mB[k] = rec[0];
+        aB[k] = rec[2 + quarter * kMergeDims + tx];
+        if (tx == 0) lB[k] = rec[1];
+      }
+    }
+  };
+  request(lo + ty);
+  float gate_in = 0.f;
+  if (MODE != 1 && gate != nullptr && ty == 0) gate_in = gate[(size_t)out_row * kHeadDim + quarter * kMergeDims + tx];
+
   // MODE 3: the score of the extra key, by the first 256 threads (one dim each)
   float x_score = -INFINITY;
   const uint8_t *x_vrow = nullptr;
@@ -71,36 +97,22 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     x_vrow = xk.v_row + (size_t)kvh * merge_row_bytes(xk.vt);
   }
 
-  // One pass: group ty walks records lo+ty, lo+ty+16, ... with four loads in flight and
-  // keeps a local log-sum-exp (m, l, acc); the 16 groups are then combined through shared
-  // memory. An empty record (m = -inf) weighs nothing and whatever its body holds is
-  // never used.
   float mloc = -INFINITY, acc = 0.f, ll = 0.f;
-  for (int s0 = lo + ty; s0 < hi; s0 += 4 * kMergeGroups) {
-    float m4[4], a4[4], l4[4];
+  for (int s0 = lo + ty; s0 < hi; s0 += kBatch * kMergeGroups) {
+    if (s0 != lo + ty) request(s0);
+    float mb = mloc;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int s = s0 + k * kMergeGroups;
-      m4[k] = -INFINITY;
-      a4[k] = l4[k] = 0.f;
-      if (s < hi) {
-        const float *rec = base + (size_t)s * kRec;
-        m4[k] = rec[0];
-        a4[k] = rec[2 + quarter * kMergeDims + tx];
-        if (tx == 0) l4[k] = rec[1];
-      }
-    }
-    const float mb = fmaxf(fmaxf(mloc, fmaxf(m4[0], m4[1])), fmaxf(m4[2], m4[3]));
+    for (int k = 0; k < kBatch; ++k) mb = fmaxf(mb, mB[k]);
     if (mb != -INFINITY) {
       const float f = expf(mloc - mb);   // 0 while nothing has been accumulated
       acc *= f;
       ll *= f;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (m4[k] != -INFINITY) {
-          const float w = expf(m4[k] - mb);
-          acc = fmaf(a4[k], w, acc);
-          ll = fmaf(l4[k], w, ll);
+      for (int k = 0; k < kBatch; ++k) {
+        if (mB[k] != -INFINITY) {
+          const float w = expf(mB[k] - mb);
+          acc = fmaf(aB[k], w, acc);
+          ll = fmaf(lB[k], w, ll);
         }
       }
       mloc = mb;
@@ -136,7 +148,7 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
       float *op = out + (size_t)out_row * kHeadDim + d;
       if (gate != nullptr) {
         float *gp = gate + (size_t)out_row * kHeadDim + d;
-        const float sg = __fdiv_rn(1.0f, 1.0f + expf(-*gp));
+        const float sg = __fdiv_rn(1.0f, 1.0f + expf(-gate_in));
         *gp = sg;
         o *= sg;
       }
