@@ -22,7 +22,7 @@ constexpr int kMergeGroups = 16;  // record groups per CTA
 // MODE 2: like 0, but row = (sequence, token, head) and the record block, split count,
 // output and gate come from the sequence's descriptor (rows_per_seq = q_len * n_head).
 template <int MODE>
-__global__ void __launch_bounds__(kMergeDims *kMergeGroups)
+__global__ void __launch_bounds__(kMergeDims *kMergeGroups, MODE == 2 ? 2 : 1)
 merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_in, int n_out,
              float *__restrict__ gate, const DecodeSeq *__restrict__ seqs, int rows_per_seq,
              const ExtraKey xk) {
@@ -56,7 +56,9 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
   // records per group -- the 148 records of a full-GPU decode in ONE round trip to L2 (four
   // per batch took three) -- and the first batch is requested before anything else, the
   // gate value with it.
-  constexpr int kBatch = 10;
+  // (the many-sequence launch has thousands of CTAs with a handful of records each: there
+  // a small batch keeps the registers low enough for two CTAs per SM)
+  constexpr int kBatch = MODE == 2 ? 4 : 10;
   float mB[kBatch], aB[kBatch], lB[kBatch];
   auto request = [&](int s0) {
 #pragma unroll
