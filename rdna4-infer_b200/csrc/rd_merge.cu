@@ -99,6 +99,10 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     x_vrow = xk.v_row + (size_t)kvh * merge_row_bytes(xk.vt);
   }
 
+  // (its value for this thread's dim: requested here, used after the groups have met)
+  float x_val = 0.f;
+  if (MODE == 3 && ty == 0) x_val = load_cache_value(x_vrow, xk.vt, quarter * kMergeDims + tx);
+
   float mloc = -INFINITY, acc = 0.f, ll = 0.f;
   for (int s0 = lo + ty; s0 < hi; s0 += kBatch * kMergeGroups) {
     if (s0 != lo + ty) request(s0);
@@ -142,7 +146,7 @@ merge_kernel(const float *__restrict__ partial, float *__restrict__ out, int n_i
     const int d = quarter * kMergeDims + tx;
     if (MODE == 3) {
       const float w = expf(x_score - mm);
-      a = fmaf(load_cache_value(x_vrow, xk.vt, d), w, a);
+      a = fmaf(x_val, w, a);
       l += w;
     }
     if (MODE != 1) {

@@ -213,6 +213,9 @@ __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n
                                                      int xvt = 0) {
   constexpr int NG = NT / 16;
   constexpr int kBatch = 8;
+  // the extra key's value, requested with the records instead of after their reduction
+  float x_val = 0.f;
+  if (xv != nullptr && threadIdx.x < kPushDims) x_val = load_cache_value(xv, xvt, quarter * kPushDims + threadIdx.x);
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const float *base = partial + (size_t)row * n_in * kRec;
   float mloc = -INFINITY, ll = 0.f;
@@ -280,7 +283,7 @@ __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n
     if (xv != nullptr) {
       const float mx = fmaxf(mm, x_score);
       const float f = mm == -INFINITY ? 0.f : expf(mm - mx), w = expf(x_score - mx);
-      a = fmaf(load_cache_value(xv, xvt, quarter * kPushDims + dx), w, a * f);
+      a = fmaf(x_val, w, a * f);
       l = fmaf(l, f, w);
       mm = mx;
     }
