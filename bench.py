@@ -785,8 +785,10 @@ def main():
                          "value_best": bytes_step * K / (min(r_dev) * 1e-3) / 1e9,
                          "e2e_mean": bytes_step * K * ROUNDS / (sum(r_e2e) * 1e-3) / 1e9,
                          "e2e_best": bytes_step * K / (min(r_e2e) * 1e-3) / 1e9}
-    out["config"]["exchange"] = exchange
-    out["config"]["layer_step"] = ("append, decode, merge: three launches" if world == 1 and args.separate_append else
+    # how this arm runs the workload (kept out of `config`, which names the workload and is
+    # the same object in the reference arm)
+    out["path"] = {"exchange": exchange}
+    out["path"]["layer_step"] = ("append, decode, merge: three launches" if world == 1 and args.separate_append else
                                    "decode with the new row's append fused + merge: two launches" if world == 1 else
                                    "one launch per rank (the owner of the newest position appends in it)")
     if rank == 0 and world == 1 and args.leg == "all":
