@@ -1153,45 +1153,41 @@ decode_kernel(const __grid_constant__ DecodeKernelArgs p) {
           if (!ok && p.status != nullptr && atomicExch(&p.status->timeout_flag, 1) == 0) p.status->where = 90;
           __threadfence();
           s_go = ok;
-          // Every CTA of the launch has read the epoch by now (it did before it arrived), so
-          // the call is counted here, off the path of the exchange: the last of the role
-          // CTAs to get here resets the counters and advances the epoch.
-          const uint32_t mine = (uint32_t)((n_roles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1);
-          if (atomicAdd(&me->merge_count, mine) + mine == (uint32_t)n_roles) {
-            me->merge_count = 0;
-            me->push_count[epoch & 1] = 0;
-            __threadfence();
-            me->epoch = epoch;
-          }
         }
         __syncthreads();
+        // Every CTA of the launch has read the epoch by now (it did before it arrived), so
+        // the call can be counted: the last of the role CTAs to get here resets the counters
+        // and advances the epoch. Done by a thread that takes no part in the merge below, so
+        // that the round trip of its atomic is on nobody's path.
+        // (the atomic is issued here and its result looked at after the exchange)
+        const uint32_t cnt_mine = (uint32_t)((n_roles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1);
+        uint32_t cnt_prev = 0;
+        if (threadIdx.x == kPushDims) cnt_prev = atomicAdd(&me->merge_count, cnt_mine);
         for (int role = blockIdx.x; role < n_roles; role += gridDim.x) {
           const int row = role / kQuarters, quarter = role % kQuarters;
           // a fused append: the new row (stored by this launch's first CTAs, not attended by
-          // any of them) joins here as one more record; its score = scale * q . k, by the
-          // first 256 threads
-          float x_score = 0.f;
+          // any of them) joins here as one more record; its score = scale * q . k: every
+          // thread requests its share of the products here, the push sums them
+          float x_prod = 0.f;
           const uint8_t *xv = nullptr;
           if (p.k_new != nullptr) {
             const int kvh_x = row / kGroup;
-            float prod = 0.f;
             for (int dd = threadIdx.x; dd < kHeadDim; dd += NT)
-              prod += __ldcg(p.q + (size_t)row * kHeadDim + dd) *
-                      load_cache_value(p.k + ((size_t)p.new_row * nkv + kvh_x) * RK, KT, dd);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(FULL, prod, o);
-            if (lane == 0) s_pgm[warp] = prod;   // scratch, rewritten by the push below
-            asm volatile("bar.sync 8, %0;" ::"r"(NT) : "memory");
-            for (int i = 0; i < NT / 32; ++i) x_score += s_pgm[i];
-            x_score *= p.qscale * 0.6931471805599453f;   // qscale = scale * log2(e): back to natural-log units
+              x_prod += __ldcg(p.q + (size_t)row * kHeadDim + dd) *
+                        load_cache_value(p.k + ((size_t)p.new_row * nkv + kvh_x) * RK, KT, dd);
             xv = p.v + ((size_t)p.new_row * nkv + kvh_x) * RV;
-            asm volatile("bar.sync 8, %0;" ::"r"(NT) : "memory");
           }
-          if (s_go)
+          if (s_go)   // qscale = scale * log2(e): x ln 2 brings the score back to natural-log units
             shard_push_part_wide<NT>(p.partial, (int)gridDim.x, p.n_head, row, quarter, p.push, epoch, s_pacc, s_pl,
-                                     s_pgm, 8, x_score, xv, VT);
+                                     s_pgm, 8, x_prod, p.qscale * 0.6931471805599453f, xv, VT);
           if (threadIdx.x < kPushDims)
             shard_merge_part(p.x_out, p.x_gate, p.n_head, row, quarter, threadIdx.x, p.push, epoch, p.status);
+        }
+        if (threadIdx.x == kPushDims && cnt_prev + cnt_mine == (uint32_t)n_roles) {
+          me->merge_count = 0;
+          me->push_count[epoch & 1] = 0;
+          __threadfence();
+          me->epoch = epoch;
         }
       }
     }

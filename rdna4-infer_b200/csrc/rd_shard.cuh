@@ -209,10 +209,14 @@ template <int NT>
 __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n_in, int n_head, int row,
                                                      int quarter, const ShardPeers &g, uint32_t epoch,
                                                      float *s_acc, float *s_l, float *s_gm, int bar_id,
-                                                     float x_score = 0.f, const uint8_t *xv = nullptr,
-                                                     int xvt = 0) {
+                                                     float x_prod = 0.f, float x_scale = 0.f,
+                                                     const uint8_t *xv = nullptr, int xvt = 0) {
   constexpr int NG = NT / 16;
   constexpr int kBatch = 8;
+  // The extra key's score = x_scale * (sum of every thread's x_prod): the caller has
+  // requested the products' operands just before this call, so their round trip runs with
+  // the one of the records; the warps' sums meet in s_xp (behind s_gm) at the barrier below.
+  float *s_xp = s_gm + NG;
   // the extra key's value, requested with the records instead of after their reduction
   float x_val = 0.f;
   if (xv != nullptr && threadIdx.x < kPushDims) x_val = load_cache_value(xv, xvt, quarter * kPushDims + threadIdx.x);
@@ -267,6 +271,11 @@ __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n
     s_l[ty] = ll;
     s_gm[ty] = mloc;
   }
+  if (xv != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x_prod += __shfl_xor_sync(0xffffffffu, x_prod, o);
+    if ((threadIdx.x & 31) == 0) s_xp[threadIdx.x >> 5] = x_prod;
+  }
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(NT) : "memory");
   if (threadIdx.x < kPushDims) {
     const int dx = threadIdx.x;
@@ -281,6 +290,9 @@ __device__ __forceinline__ void shard_push_part_wide(const float *partial, int n
       }
     }
     if (xv != nullptr) {
+      float x_score = 0.f;
+      for (int i = 0; i < NT / 32; ++i) x_score += s_xp[i];
+      x_score *= x_scale;
       const float mx = fmaxf(mm, x_score);
       const float f = mm == -INFINITY ? 0.f : expf(mm - mx), w = expf(x_score - mx);
       a = fmaf(x_val, w, a * f);
